@@ -1,0 +1,127 @@
+/*
+ * libmoc_b200 - C ABI of the B200 (sm_100a) implementation of the Mixture-of-Channels sparse
+ * SwiGLU FFN path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless said otherwise; the library allocates nothing,
+ *     keeps no reference to caller memory and launches on the stream it is given
+ *     (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *   - Functions return 0 on success or a negative MOC_ERR_* code, never throw and never
+ *     exit; moc_last_error() gives the text of the calling thread's last failure.
+ *   - dtype: MOC_BF16 (tensor-core path, tcgen05) or MOC_F32 (CUDA-core path). All tensors
+ *     of one call share the dtype; indices are int16, masks uint32, ranks uint16.
+ *   - Matrices are row-major and contiguous unless a leading dimension is given.
+ *   - "tokens" = rows of the flattened activation x[tokens, d]; d = hidden size,
+ *     d_ffn = intermediate size (F), k = selected channels per token.
+ *
+ * Each entry point names the reference interface it replaces (path:line inside
+ * xiaohuangji/MoC).
+ */
+#ifndef MOC_B200_H_
+#define MOC_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOC_B200_ABI_VERSION 1
+
+#define MOC_BF16 0
+#define MOC_F32 1
+
+#define MOC_OK 0
+#define MOC_ERR_INVALID_ARG (-1)
+#define MOC_ERR_UNSUPPORTED (-2)
+#define MOC_ERR_WORKSPACE (-3)
+#define MOC_ERR_CUDA (-4)
+#define MOC_ERR_TENSOR_MAP (-5)
+#define MOC_ERR_DEVICE_TIMEOUT (-6)
+
+/* channel selection rule */
+#define MOC_SELECT_TOPK 0   /* global row-wise Top-K on the pre-SiLU gate (moc/ffn.py:144) */
+#define MOC_SELECT_2OF8 1   /* top-2 of every 8 consecutive channels (moc/ffn.py:68-108) */
+
+int moc_b200_abi_version(void);
+
+/* Text of the last error raised on the calling host thread ("" if none). */
+const char* moc_last_error(void);
+
+/* Layout helpers: leading dimension (elements) of dense [tokens, d_ffn] scratch rows,
+ * 32-bit mask words per token, and K' of the 2:8 rule (moc/ffn.py:62-65). */
+int64_t moc_ffn_ld(int64_t d_ffn);
+int64_t moc_mask_words(int64_t d_ffn);
+int64_t moc_select_2of8_k(int64_t d_ffn);
+
+/* Workspace sizes in bytes for moc_ffn_fwd / moc_ffn_bwd (256-byte aligned base). */
+int64_t moc_ffn_fwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn);
+int64_t moc_ffn_bwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn);
+
+/* out[cols, rows] = in[rows, cols]^T. Used to keep W_down^T [d_ffn, d] next to the
+ * parameter W_down [d, d_ffn]; replaces `down_proj.weight.t().contiguous()`
+ * (moc/inference/inference_ffn.py:104-110). */
+int moc_transpose(int dtype, const void* in, void* out, int64_t rows, int64_t cols, void* stream);
+
+/* Row-wise Top-K channel selection on a gate matrix g[tokens, ldg] (first d_ffn columns).
+ * Outputs, per token: idx[k] selected channels in ascending order, g_sel[k] their gate
+ * values, bitmap[moc_mask_words] selection mask, rank0[moc_mask_words] rank of each mask
+ * word's first channel. Ties at the K-th value go to the lower channel index; values are
+ * ordered by the IEEE total order. Replaces torch.topk(g, k, dim=-1, sorted=False) +
+ * _pack_topk_idx (moc/ffn.py:144-147, :27-41) and cub_topk_idx_i32_bf16_kernel
+ * (moc/inference/cuda/optimized_global_moc_ext.cu:85-125). d_ffn <= 32768. */
+int moc_topk_select(int dtype, const void* g, int64_t ldg, int64_t tokens, int64_t d_ffn, int64_t k,
+                    int16_t* idx, void* g_sel, uint32_t* bitmap, uint16_t* rank0, void* stream);
+
+/* Structured selection, k = moc_select_2of8_k(d_ffn). Replaces _select_moc_2_8
+ * (moc/ffn.py:68-108) and the in-kernel top-2 of
+ * moc/inference/triton_fused_ffn_kernels.py:95-114. */
+int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64_t d_ffn, int16_t* idx,
+                    void* g_sel, uint32_t* bitmap, uint16_t* rank0, void* stream);
+
+/* C[m, n] = A[m, k] * B[n, k]^T with fp32 accumulation. a_mn / b_mn = 1 when the operand is
+ * stored [k][m] / [k][n] (M or N contiguous) instead of [m][k] / [n][k]. c_transposed = 1
+ * stores C^T (C[j * ldc + i]). impl: 0 = default core of the dtype (bf16: tcgen05 / TMEM,
+ * f32: CUDA cores), 1 = CUDA-core core for either dtype. status: one device int, zeroed by
+ * the caller, receives a code if a bounded device-side wait gives up. Stands in for the
+ * `@` / nn.Linear calls of moc/ffn.py:141-163, :203-254. */
+int moc_gemm(int dtype, int impl, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_mn,
+             const void* b, int64_t ldb, int b_mn, void* c, int64_t ldc, int c_transposed, int* status,
+             void* stream);
+
+/* MoC FFN forward: y = (mask(SiLU(x Wg^T)) * (x Wu^T)) Wd^T with the mask chosen by
+ * `select`. Replaces _MoCFunction.forward / _MoCGCPFunction.forward / _MoC28Function.forward
+ * (moc/ffn.py:130-173, :378-421, :266-308) including sparse_forward_aux
+ * (moc/training/triton_sparse_aux.py:197-231).
+ *   in : x[tokens, d], w_gate[d_ffn, d], w_up[d_ffn, d], w_down_t[d_ffn, d] (= W_down^T)
+ *   out: y[tokens, d]; the saved activation set idx[tokens, k], g_sel, u_sel [tokens, k],
+ *        optional s_sel, z_sel [tokens, k] (pass NULL for moc_gcp), bitmap / rank0
+ *        [tokens, moc_mask_words(d_ffn)].
+ * The dense G / Z' scratch lives in `workspace`; its first 256 bytes are a status area. */
+int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* x,
+                const void* w_gate, const void* w_up, const void* w_down_t, void* y, int16_t* idx, void* g_sel,
+                void* u_sel, void* s_sel, void* z_sel, uint32_t* bitmap, uint16_t* rank0, void* workspace,
+                int64_t workspace_bytes, void* stream);
+
+/* MoC FFN backward. Replaces _MoCFunction.backward / _MoCGCPFunction.backward
+ * (moc/ffn.py:176-259, :424-497) including scatter_sparse_to_dense and sparse_backward_aux
+ * (moc/training/triton_sparse_aux.py:266-423). s_sel / z_sel NULL = recompute them from
+ * g_sel, u_sel (moc_gcp). Outputs are overwritten, not accumulated: grad_x[tokens, d],
+ * grad_w_gate[d_ffn, d], grad_w_up[d_ffn, d], grad_w_down[d, d_ffn] (parameter layout).
+ * ev_down / ev_gate / ev_up: optional cudaEvent_t handles recorded on `stream` as soon as the
+ * respective weight gradient is final, so a caller can start its all-reduce while the rest of
+ * the backward pass runs. */
+int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* grad_y, const void* x,
+                const void* w_gate, const void* w_up, const void* w_down_t, const uint32_t* bitmap,
+                const uint16_t* rank0, const void* g_sel, const void* u_sel, const void* s_sel, const void* z_sel,
+                void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
+                int64_t workspace_bytes, void* ev_down, void* ev_gate, void* ev_up, void* stream);
+
+/* Synchronises `stream` and returns MOC_OK, or MOC_ERR_DEVICE_TIMEOUT if a kernel of the
+ * last call that used `workspace` recorded a bounded-wait failure in its status area. */
+int moc_read_status(const void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOC_B200_H_ */

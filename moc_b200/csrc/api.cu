@@ -1,0 +1,351 @@
+// C ABI of libmoc_b200: argument checks and the launch sequences of the MoC FFN
+// forward / backward passes. Declarations and reference citations: include/moc_b200.h.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/moc_b200.h"
+#include "common.cuh"
+#include "internal.h"
+
+namespace moc {
+const char* last_error_text();
+}
+
+using namespace moc;
+
+namespace {
+
+constexpr int64_t kStatusBytes = 256;
+
+inline size_t esize(int dtype) { return dtype == kBF16 ? 2 : 4; }
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+bool bad_dtype(int dtype) {
+  if (dtype == kBF16 || dtype == kF32) return false;
+  set_error("unsupported dtype code %d", dtype);
+  return true;
+}
+
+int check_dims(int64_t tokens, int64_t d, int64_t d_ffn, int64_t k) {
+  if (tokens < 0 || d <= 0 || d_ffn <= 0 || k <= 0 || k > d_ffn) {
+    set_error("bad sizes: tokens=%lld d=%lld d_ffn=%lld k=%lld", (long long)tokens, (long long)d, (long long)d_ffn,
+              (long long)k);
+    return kErrInvalidArg;
+  }
+  if (d_ffn > 32768) {
+    set_error("d_ffn=%lld: channel indices are stored as int16, d_ffn must be <= 32768", (long long)d_ffn);
+    return kErrUnsupported;
+  }
+  if (tokens > (int64_t(1) << 30) || d > (int64_t(1) << 24)) {
+    set_error("sizes exceed the 32-bit tile arithmetic of the kernels");
+    return kErrUnsupported;
+  }
+  return kOk;
+}
+
+MatOperand operand(const void* p, int64_t ld, int mn_major) {
+  MatOperand o;
+  o.ptr = p;
+  o.ld = ld;
+  o.mn_major = mn_major;
+  return o;
+}
+
+EpiArgs store_epi(void* c, int64_t ldc, int transposed) {
+  EpiArgs e = {};
+  e.kind = kEpiStore;
+  e.c = c;
+  e.ldc = ldc;
+  e.transposed = transposed;
+  return e;
+}
+
+int record(void* ev, cudaStream_t stream) {
+  if (!ev) return kOk;
+  if (cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev), stream) != cudaSuccess) return check_last("cudaEventRecord");
+  return kOk;
+}
+
+}  // namespace
+
+extern "C" {
+
+int moc_b200_abi_version(void) { return MOC_B200_ABI_VERSION; }
+
+const char* moc_last_error(void) { return last_error_text(); }
+
+int64_t moc_ffn_ld(int64_t d_ffn) { return ffn_ld(d_ffn); }
+int64_t moc_mask_words(int64_t d_ffn) { return mask_words(d_ffn); }
+int64_t moc_select_2of8_k(int64_t d_ffn) { return (d_ffn / 8) * 2 + (d_ffn % 8 < 2 ? d_ffn % 8 : 2); }
+
+int64_t moc_ffn_fwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
+  return kStatusBytes + round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
+}
+int64_t moc_ffn_bwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
+  return kStatusBytes + 2 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
+}
+
+int moc_transpose(int dtype, const void* in, void* out, int64_t rows, int64_t cols, void* stream) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  if (!in || !out || rows < 0 || cols < 0) {
+    set_error("moc_transpose: null pointer or negative size");
+    return kErrInvalidArg;
+  }
+  return launch_transpose(dtype, in, cols, out, rows, (int)rows, (int)cols, as_stream(stream));
+}
+
+int moc_topk_select(int dtype, const void* g, int64_t ldg, int64_t tokens, int64_t d_ffn, int64_t k, int16_t* idx,
+                    void* g_sel, uint32_t* bitmap, uint16_t* rank0, void* stream) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  int rc = check_dims(tokens, 1, d_ffn, k);
+  if (rc != kOk) return rc;
+  if (!g || !idx || !g_sel || !bitmap || !rank0 || ldg < d_ffn) {
+    set_error("moc_topk_select: null pointer or ldg < d_ffn");
+    return kErrInvalidArg;
+  }
+  return launch_topk_select(dtype, g, ldg, (int)tokens, (int)d_ffn, (int)k, idx, g_sel, bitmap, rank0,
+                            as_stream(stream));
+}
+
+int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64_t d_ffn, int16_t* idx, void* g_sel,
+                    uint32_t* bitmap, uint16_t* rank0, void* stream) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  int rc = check_dims(tokens, 1, d_ffn, 1);
+  if (rc != kOk) return rc;
+  if (!g || !idx || !g_sel || !bitmap || !rank0 || ldg < d_ffn) {
+    set_error("moc_select_2of8: null pointer or ldg < d_ffn");
+    return kErrInvalidArg;
+  }
+  return launch_select_2of8(dtype, g, ldg, (int)tokens, (int)d_ffn, idx, g_sel, bitmap, rank0, as_stream(stream));
+}
+
+int moc_gemm(int dtype, int impl, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_mn,
+             const void* b, int64_t ldb, int b_mn, void* c, int64_t ldc, int c_transposed, int* status,
+             void* stream) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  if (m < 0 || n < 0 || k <= 0 || !a || !b || !c || m > (int64_t(1) << 30) || n > (int64_t(1) << 30) ||
+      k > (int64_t(1) << 30)) {
+    set_error("moc_gemm: bad sizes or null pointer");
+    return kErrInvalidArg;
+  }
+  GemmProblem p = {};
+  p.dtype = dtype;
+  p.impl = impl;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.k0 = (int)k;
+  p.a0 = operand(a, lda, a_mn);
+  p.b0 = operand(b, ldb, b_mn);
+  p.k1 = 0;
+  p.epi = store_epi(c, ldc, c_transposed);
+  p.status = status;
+  return launch_gemm(p, as_stream(stream));
+}
+
+int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* x,
+                const void* w_gate, const void* w_up, const void* w_down_t, void* y, int16_t* idx, void* g_sel,
+                void* u_sel, void* s_sel, void* z_sel, uint32_t* bitmap, uint16_t* rank0, void* workspace,
+                int64_t workspace_bytes, void* stream_) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  int rc = check_dims(tokens, d, d_ffn, k);
+  if (rc != kOk) return rc;
+  if (!x || !w_gate || !w_up || !w_down_t || !y || !idx || !g_sel || !u_sel || !bitmap || !rank0 || !workspace) {
+    set_error("moc_ffn_fwd: null pointer");
+    return kErrInvalidArg;
+  }
+  if (select != MOC_SELECT_TOPK && select != MOC_SELECT_2OF8) {
+    set_error("moc_ffn_fwd: unknown selection rule %d", select);
+    return kErrInvalidArg;
+  }
+  if (select == MOC_SELECT_2OF8 && k != moc_select_2of8_k(d_ffn)) {
+    set_error("moc_ffn_fwd: the 2:8 rule selects k=%lld channels for d_ffn=%lld, got k=%lld",
+              (long long)moc_select_2of8_k(d_ffn), (long long)d_ffn, (long long)k);
+    return kErrInvalidArg;
+  }
+  if (workspace_bytes < moc_ffn_fwd_workspace_bytes(dtype, tokens, d_ffn) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    set_error("moc_ffn_fwd: workspace too small (%lld < %lld bytes) or not 256-byte aligned",
+              (long long)workspace_bytes, (long long)moc_ffn_fwd_workspace_bytes(dtype, tokens, d_ffn));
+    return kErrWorkspace;
+  }
+  cudaStream_t stream = as_stream(stream_);
+  int* status = static_cast<int*>(workspace);
+  if (cudaMemsetAsync(status, 0, kStatusBytes, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
+  if (tokens == 0) return kOk;
+  void* dense = static_cast<uint8_t*>(workspace) + kStatusBytes;
+  const int64_t ld = ffn_ld(d_ffn);
+  const int words = (int)mask_words(d_ffn);
+
+  // G = X Wg^T (moc/ffn.py:141), rounded to the storage type, rows padded to ld
+  GemmProblem p = {};
+  p.dtype = dtype;
+  p.m = (int)tokens;
+  p.n = (int)d_ffn;
+  p.k0 = (int)d;
+  p.a0 = operand(x, d, 0);
+  p.b0 = operand(w_gate, d, 0);
+  p.epi = store_epi(dense, ld, 0);
+  p.status = status;
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+
+  // channel selection on the rounded G (moc/ffn.py:144-147)
+  if (select == MOC_SELECT_TOPK)
+    rc = launch_topk_select(dtype, dense, ld, (int)tokens, (int)d_ffn, (int)k, idx, g_sel, bitmap, rank0, stream);
+  else
+    rc = launch_select_2of8(dtype, dense, ld, (int)tokens, (int)d_ffn, idx, g_sel, bitmap, rank0, stream);
+  if (rc != kOk) return rc;
+
+  // U = X Wu^T with the selected-activation epilogue; G is overwritten by Z' (moc/ffn.py:146-161)
+  p.b0 = operand(w_up, d, 0);
+  p.epi = EpiArgs{};
+  p.epi.kind = kEpiUpSparse;
+  p.epi.dense0 = dense;
+  p.epi.ld_dense = ld;
+  p.epi.bitmap = bitmap;
+  p.epi.rank0 = rank0;
+  p.epi.words = words;
+  p.epi.k_sel = (int)k;
+  p.epi.u_sel = u_sel;
+  p.epi.s_sel = s_sel;
+  p.epi.z_sel = z_sel;
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+
+  // Y = Z' Wd^T (moc/ffn.py:163): A = Z' [tokens, F] K-major, B = W_down^T [F, d] N-contiguous
+  GemmProblem q = {};
+  q.dtype = dtype;
+  q.m = (int)tokens;
+  q.n = (int)d;
+  q.k0 = (int)d_ffn;
+  q.a0 = operand(dense, ld, 0);
+  q.b0 = operand(w_down_t, d, 1);
+  q.epi = store_epi(y, d, 0);
+  q.status = status;
+  return launch_gemm(q, stream);
+}
+
+int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* grad_y, const void* x,
+                const void* w_gate, const void* w_up, const void* w_down_t, const uint32_t* bitmap,
+                const uint16_t* rank0, const void* g_sel, const void* u_sel, const void* s_sel, const void* z_sel,
+                void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
+                int64_t workspace_bytes, void* ev_down, void* ev_gate, void* ev_up, void* stream_) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  int rc = check_dims(tokens, d, d_ffn, k);
+  if (rc != kOk) return rc;
+  if (!grad_y || !x || !w_gate || !w_up || !w_down_t || !bitmap || !rank0 || !g_sel || !u_sel || !grad_x ||
+      !grad_w_gate || !grad_w_up || !grad_w_down || !workspace) {
+    set_error("moc_ffn_bwd: null pointer");
+    return kErrInvalidArg;
+  }
+  if (workspace_bytes < moc_ffn_bwd_workspace_bytes(dtype, tokens, d_ffn) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    set_error("moc_ffn_bwd: workspace too small (%lld < %lld bytes) or not 256-byte aligned",
+              (long long)workspace_bytes, (long long)moc_ffn_bwd_workspace_bytes(dtype, tokens, d_ffn));
+    return kErrWorkspace;
+  }
+  cudaStream_t stream = as_stream(stream_);
+  int* status = static_cast<int*>(workspace);
+  if (cudaMemsetAsync(status, 0, kStatusBytes, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
+  const size_t es = esize(dtype);
+  if (tokens == 0) {
+    // no tokens: every gradient is zero
+    if (cudaMemsetAsync(grad_w_gate, 0, (size_t)d_ffn * d * es, stream) != cudaSuccess ||
+        cudaMemsetAsync(grad_w_up, 0, (size_t)d_ffn * d * es, stream) != cudaSuccess ||
+        cudaMemsetAsync(grad_w_down, 0, (size_t)d_ffn * d * es, stream) != cudaSuccess)
+      return check_last("cudaMemsetAsync");
+    if ((rc = record(ev_down, stream)) != kOk || (rc = record(ev_gate, stream)) != kOk ||
+        (rc = record(ev_up, stream)) != kOk)
+      return rc;
+    return kOk;
+  }
+  const int64_t ld = ffn_ld(d_ffn);
+  const int words = (int)mask_words(d_ffn);
+  const int64_t dense_bytes = round_up_i64(tokens * ld * (int64_t)es, 256);
+  void* buf_a = static_cast<uint8_t*>(workspace) + kStatusBytes;
+  void* buf_b = static_cast<uint8_t*>(buf_a) + dense_bytes;
+
+  // Z' from the saved (or recomputed) selected activations (moc/ffn.py:196-199, :435-442)
+  if ((rc = launch_expand_z(dtype, bitmap, rank0, z_sel, g_sel, u_sel, buf_a, ld, (int)tokens, (int)d_ffn, (int)k,
+                            stream)) != kOk)
+    return rc;
+
+  // dW_down[d, F] = dY^T Z' (moc/ffn.py:203), computed as the [F, d] product Z'^T dY and
+  // stored transposed so that warps write along the channel dimension.
+  GemmProblem p = {};
+  p.dtype = dtype;
+  p.status = status;
+  p.m = (int)d_ffn;
+  p.n = (int)d;
+  p.k0 = (int)tokens;
+  p.a0 = operand(buf_a, ld, 1);
+  p.b0 = operand(grad_y, d, 1);
+  p.epi = store_epi(grad_w_down, d_ffn, 1);
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+  if ((rc = record(ev_down, stream)) != kOk) return rc;
+
+  // dZ = dY W_down (moc/ffn.py:206) with the gather + SiLU' epilogue -> dense dG', dU' (moc/ffn.py:209-237)
+  GemmProblem z = {};
+  z.dtype = dtype;
+  z.status = status;
+  z.m = (int)tokens;
+  z.n = (int)d_ffn;
+  z.k0 = (int)d;
+  z.a0 = operand(grad_y, d, 0);
+  z.b0 = operand(w_down_t, d, 0);
+  z.epi.kind = kEpiBwdSparse;
+  z.epi.dense0 = buf_a;
+  z.epi.dense1 = buf_b;
+  z.epi.ld_dense = ld;
+  z.epi.bitmap = bitmap;
+  z.epi.rank0 = rank0;
+  z.epi.words = words;
+  z.epi.k_sel = (int)k;
+  z.epi.g_sel = g_sel;
+  z.epi.u_sel = const_cast<void*>(u_sel);
+  z.epi.s_sel = const_cast<void*>(s_sel);
+  if ((rc = launch_gemm(z, stream)) != kOk) return rc;
+
+  // dW_gate = dG'^T X, dW_up = dU'^T X (moc/ffn.py:239-253)
+  p.epi = store_epi(grad_w_gate, d, 0);
+  p.a0 = operand(buf_a, ld, 1);
+  p.b0 = operand(x, d, 1);
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+  if ((rc = record(ev_gate, stream)) != kOk) return rc;
+  p.epi = store_epi(grad_w_up, d, 0);
+  p.a0 = operand(buf_b, ld, 1);
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+  if ((rc = record(ev_up, stream)) != kOk) return rc;
+
+  // dX = dG' W_gate + dU' W_up (moc/ffn.py:245-255), one accumulator over two K segments
+  GemmProblem gx = {};
+  gx.dtype = dtype;
+  gx.status = status;
+  gx.m = (int)tokens;
+  gx.n = (int)d;
+  gx.k0 = (int)d_ffn;
+  gx.a0 = operand(buf_a, ld, 0);
+  gx.b0 = operand(w_gate, d, 1);
+  gx.k1 = (int)d_ffn;
+  gx.a1 = operand(buf_b, ld, 0);
+  gx.b1 = operand(w_up, d, 1);
+  gx.epi = store_epi(grad_x, d, 0);
+  return launch_gemm(gx, stream);
+}
+
+int moc_read_status(const void* workspace, void* stream_) {
+  if (!workspace) {
+    set_error("moc_read_status: null workspace");
+    return kErrInvalidArg;
+  }
+  int word = 0;
+  cudaStream_t stream = as_stream(stream_);
+  if (cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return check_last("moc_read_status");
+  if (word != 0) {
+    set_error("device-side wait timed out: role %d, detail 0x%x", (word >> 24) & 0xFF, word & 0xFFFFFF);
+    return kErrDeviceTimeout;
+  }
+  return kOk;
+}
+
+}  // extern "C"

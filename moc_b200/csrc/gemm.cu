@@ -1,0 +1,264 @@
+// Host-side GEMM dispatch: builds the TMA descriptors, picks the core (tcgen05 for bf16,
+// CUDA cores for fp32) and instantiates the epilogue functors.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "epilogues.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_tcgen05.cuh"
+#include "internal.h"
+
+namespace moc {
+
+// ---- error text (thread-local, read through moc_last_error) ---------------------------------
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+const char* last_error_text() { return g_err; }
+
+int check_last(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return kErrCuda;
+  }
+  return kOk;
+}
+
+// ---- driver entry point for tensor-map encoding (no link-time dependency on libcuda) -----------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// bf16 operand of extent [mn_extent, k_extent]; tile_mn = rows of the CTA tile it feeds.
+static int make_operand_map(CUtensorMap* tm, const MatOperand& op, int64_t mn_extent, int64_t k_extent, int tile_mn) {
+  auto encode = get_encode_fn();
+  if (!encode) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return kErrCuda;
+  }
+  if ((reinterpret_cast<uintptr_t>(op.ptr) & 15u) != 0 || (op.ld * 2) % 16 != 0) {
+    set_error("GEMM operand needs a 16-byte aligned base and a leading dimension that is a multiple of 8 "
+              "(ptr=%p ld=%lld)", op.ptr, static_cast<long long>(op.ld));
+    return kErrUnsupported;
+  }
+  cuuint64_t dims[2], strides[1];
+  cuuint32_t box[2], estr[2] = {1, 1};
+  if (!op.mn_major) {
+    dims[0] = static_cast<cuuint64_t>(k_extent);
+    dims[1] = static_cast<cuuint64_t>(mn_extent);
+    box[0] = kBlockK;
+    box[1] = static_cast<cuuint32_t>(tile_mn);
+  } else {
+    dims[0] = static_cast<cuuint64_t>(mn_extent);
+    dims[1] = static_cast<cuuint64_t>(k_extent);
+    box[0] = 64;
+    box[1] = kBlockK;
+  }
+  strides[0] = static_cast<cuuint64_t>(op.ld) * 2;
+  const CUresult r = encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(op.ptr), dims, strides, box,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d (dims %llu x %llu, ld %lld)", static_cast<int>(r),
+              static_cast<unsigned long long>(dims[0]), static_cast<unsigned long long>(dims[1]),
+              static_cast<long long>(op.ld));
+    return kErrTensorMap;
+  }
+  return kOk;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <class Epi>
+static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
+  if (!p.status) {
+    set_error("tcgen05 GEMM needs a device status word");
+    return kErrInvalidArg;
+  }
+  CUtensorMap ta0, tb0, ta1, tb1;
+  int rc;
+  if ((rc = make_operand_map(&ta0, p.a0, p.m, p.k0, kBlockM)) != kOk) return rc;
+  if ((rc = make_operand_map(&tb0, p.b0, p.n, p.k0, kBlockN)) != kOk) return rc;
+  if (p.k1 > 0) {
+    if ((rc = make_operand_map(&ta1, p.a1, p.m, p.k1, kBlockM)) != kOk) return rc;
+    if ((rc = make_operand_map(&tb1, p.b1, p.n, p.k1, kBlockN)) != kOk) return rc;
+    if (p.a1.mn_major != p.a0.mn_major || p.b1.mn_major != p.b0.mn_major) {
+      set_error("both K segments must use the same operand majors");
+      return kErrUnsupported;
+    }
+  } else {
+    ta1 = ta0;
+    tb1 = tb0;
+  }
+  GemmShape sh;
+  sh.m = p.m;
+  sh.n = p.n;
+  sh.kb0 = ceil_div_i(p.k0, kBlockK);
+  sh.kb1 = p.k1 > 0 ? ceil_div_i(p.k1, kBlockK) : 0;
+  sh.a_mn = p.a0.mn_major;
+  sh.b_mn = p.b0.mn_major;
+  sh.tiles_m = ceil_div_i(p.m, kBlockM);
+  sh.tiles_n = ceil_div_i(p.n, kBlockN);
+  sh.status = p.status;
+  auto kern = gemm_tcgen05_kernel<Epi>;
+  static thread_local const void* configured = nullptr;
+  if (configured != reinterpret_cast<const void*>(kern)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) != cudaSuccess)
+      return check_last("gemm smem attribute");
+    configured = reinterpret_cast<const void*>(kern);
+  }
+  const int tiles = sh.tiles_m * sh.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ta0, tb0, ta1, tb1, sh, epi);
+  return check_last("gemm_tcgen05");
+}
+
+template <typename T>
+static SimtOperand<T> simt_operand(const MatOperand& op) {
+  SimtOperand<T> o;
+  o.p = static_cast<const T*>(op.ptr);
+  o.s_mn = op.mn_major ? 1 : op.ld;
+  o.s_k = op.mn_major ? op.ld : 1;
+  return o;
+}
+
+template <typename T, class Epi>
+static int launch_simt(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
+  const dim3 grid(ceil_div_i(p.n, kSimtBN), ceil_div_i(p.m, kSimtBM));
+  SimtOperand<T> a0 = simt_operand<T>(p.a0), b0 = simt_operand<T>(p.b0);
+  SimtOperand<T> a1 = p.k1 > 0 ? simt_operand<T>(p.a1) : a0;
+  SimtOperand<T> b1 = p.k1 > 0 ? simt_operand<T>(p.b1) : b0;
+  gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(a0, b0, p.k0, a1, b1, p.k1 > 0 ? p.k1 : 0, p.m, p.n,
+                                                              epi);
+  return check_last("gemm_simt");
+}
+
+template <typename T, class Epi>
+static int launch_core(const GemmProblem& p, const Epi& epi, cudaStream_t stream);
+
+template <class Epi>
+static int launch_core_bf16(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
+  if (p.impl == 1) return launch_simt<__nv_bfloat16, Epi>(p, epi, stream);
+  return launch_tcgen05<Epi>(p, epi, stream);
+}
+
+template <typename T>
+static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
+  const EpiArgs& e = p.epi;
+  auto run = [&](auto epi) -> int {
+    using E = decltype(epi);
+    if constexpr (Num<T>::kIsBf16) return launch_core_bf16<E>(p, epi, stream);
+    else return launch_simt<T, E>(p, epi, stream);
+  };
+  const bool dense_aligned = (reinterpret_cast<uintptr_t>(e.dense0) & 15u) == 0 &&
+                             (reinterpret_cast<uintptr_t>(e.dense1) & 15u) == 0 && e.ld_dense % 64 == 0;
+  switch (e.kind) {
+    case kEpiStore: {
+      EpiStore<T> epi;
+      epi.c = static_cast<T*>(e.c);
+      epi.ldc = e.ldc;
+      epi.n = p.n;
+      epi.transposed = e.transposed;
+      epi.vec_ok = (!e.transposed && (reinterpret_cast<uintptr_t>(e.c) & 15u) == 0 &&
+                    (e.ldc * static_cast<int64_t>(sizeof(T))) % 16 == 0)
+                       ? 1
+                       : 0;
+      return run(epi);
+    }
+    case kEpiUpSparse: {
+      if (!dense_aligned) {
+        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 64");
+        return kErrWorkspace;
+      }
+      EpiUpSparse<T> epi;
+      epi.gz = static_cast<T*>(e.dense0);
+      epi.ld = e.ld_dense;
+      epi.bitmap = e.bitmap;
+      epi.rank0 = e.rank0;
+      epi.words = e.words;
+      epi.k = e.k_sel;
+      epi.u_sel = static_cast<T*>(e.u_sel);
+      epi.s_sel = static_cast<T*>(e.s_sel);
+      epi.z_sel = static_cast<T*>(e.z_sel);
+      return run(epi);
+    }
+    case kEpiBwdSparse: {
+      if (!dense_aligned) {
+        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 64");
+        return kErrWorkspace;
+      }
+      EpiBwdSparse<T> epi;
+      epi.grad_g = static_cast<T*>(e.dense0);
+      epi.grad_u = static_cast<T*>(e.dense1);
+      epi.ld = e.ld_dense;
+      epi.bitmap = e.bitmap;
+      epi.rank0 = e.rank0;
+      epi.words = e.words;
+      epi.k = e.k_sel;
+      epi.g_sel = static_cast<const T*>(e.g_sel);
+      epi.u_sel = static_cast<const T*>(e.u_sel);
+      epi.s_sel = static_cast<const T*>(e.s_sel);
+      return run(epi);
+    }
+    case kEpiDenseSwiGLU: {
+      if (!dense_aligned) {
+        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 64");
+        return kErrWorkspace;
+      }
+      EpiDenseSwiGLU<T> epi;
+      epi.gz = static_cast<T*>(e.dense0);
+      epi.u_out = static_cast<T*>(e.dense1);
+      epi.ld = e.ld_dense;
+      return run(epi);
+    }
+    default:
+      set_error("unknown epilogue kind %d", e.kind);
+      return kErrInvalidArg;
+  }
+}
+
+int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
+  if (p.m <= 0 || p.n <= 0) return kOk;
+  if (p.k0 <= 0 || !p.a0.ptr || !p.b0.ptr) {
+    set_error("GEMM needs K >= 1 and non-null operands");
+    return kErrInvalidArg;
+  }
+  if (p.dtype == kBF16) return dispatch_epilogue<__nv_bfloat16>(p, stream);
+  if (p.dtype == kF32) return dispatch_epilogue<float>(p, stream);
+  set_error("unsupported dtype %d", p.dtype);
+  return kErrInvalidArg;
+}
+
+}  // namespace moc

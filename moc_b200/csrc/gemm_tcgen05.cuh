@@ -1,0 +1,236 @@
+// bf16 GEMM core for sm_100a: C[M,N] = sum over up to two K segments of A_s[M,K_s] * B_s[N,K_s]^T,
+// fp32 accumulation in tensor memory, fused epilogue functor.
+//
+//   * persistent: one CTA per SM walks output tiles of 128 x 256;
+//   * warp 0 = TMA producer (4-stage ring of 128-byte-swizzled A/B tiles, BLOCK_K = 64),
+//     warp 1 = tcgen05.mma issuer (one elected thread; also owns the TMEM allocation),
+//     warps 2-5 = epilogue (each reads its 32-lane TMEM quadrant with tcgen05.ld);
+//   * two 256-column TMEM accumulators, so the epilogue of tile i overlaps the MMAs of
+//     tile i + 1;
+//   * both operands may be K-major (K contiguous in memory) or MN-major (M/N contiguous),
+//     which covers X*W^T, dY*W and the dW = act^T * X products without any transposed copy;
+//   * the optional second K segment accumulates a second product into the same tile
+//     (dX = dG'*W_gate + dU'*W_up, moc/ffn.py:245-255) before the epilogue runs;
+//   * every mbarrier wait is bounded: on a time-out the kernel records a code in the
+//     status word, all roles leave their loops, TMEM is released and the kernel returns.
+//
+// These GEMMs stand in for the cuBLAS calls of the reference path (moc/ffn.py:141, :146,
+// :163, :203-206, :239-254).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace moc {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle span
+constexpr int kUmmaK = 16;
+constexpr int kStages = 4;
+constexpr int kTileABytes = kBlockM * kBlockK * 2;   // 16 KiB
+constexpr int kTileBBytes = kBlockN * kBlockK * 2;   // 32 KiB
+constexpr int kStageBytes = kTileABytes + kTileBBytes;
+constexpr int kMnBoxBytes = 64 * kBlockK * 2;        // one MN-major TMA box: 64 (mn) x 64 (k)
+constexpr int kTmemCols = 512;
+constexpr int kGemmThreads = 192;
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmShape {
+  int m, n;          // extents of C
+  int kb0, kb1;      // number of 64-wide k-blocks in segment 0 / 1 (kb1 == 0: single product)
+  int a_mn, b_mn;    // 1 = operand is MN-major in memory
+  int tiles_m, tiles_n;
+  int* status;       // device status word
+};
+
+template <class Epi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_b0,
+                    const __grid_constant__ CUtensorMap tm_a1, const __grid_constant__ CUtensorMap tm_b1,
+                    const GemmShape sh, const Epi epi) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;                  // [kStages] TMA -> MMA
+  uint64_t* empty_bar = bars + kStages;       // [kStages] MMA -> TMA
+  uint64_t* tfull_bar = bars + 2 * kStages;   // [2] MMA -> epilogue
+  uint64_t* tempty_bar = tfull_bar + 2;       // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = sh.tiles_m * sh.tiles_n;
+  const int kb_total = sh.kb0 + sh.kb1;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_a0);
+    ptx::prefetch_tensormap(&tm_b0);
+    if (sh.kb1 > 0) {
+      ptx::prefetch_tensormap(&tm_a1);
+      ptx::prefetch_tensormap(&tm_b1);
+    }
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    ptx::mbar_init(&tfull_bar[0], 1);
+    ptx::mbar_init(&tfull_bar[1], 1);
+    ptx::mbar_init(&tempty_bar[0], 128);
+    ptx::mbar_init(&tempty_bar[1], 128);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_alloc_permit();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / sh.tiles_n) * kBlockM;
+        const int n0 = (tile % sh.tiles_n) * kBlockN;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(sh.status, 0, (kDevTimeoutProducer << 24) | (it & 0xFFFFFF));
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+          const bool seg1 = kb >= sh.kb0;
+          const int kk = (seg1 ? kb - sh.kb0 : kb) * kBlockK;
+          const CUtensorMap* ta = seg1 ? &tm_a1 : &tm_a0;
+          const CUtensorMap* tb = seg1 ? &tm_b1 : &tm_b0;
+          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sb = sa + kTileABytes;
+          if (!sh.a_mn) {
+            ptx::tma_load_2d(sa, ta, &full_bar[s], kk, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kBlockM / 64; ++i)
+              ptx::tma_load_2d(sa + i * kMnBoxBytes, ta, &full_bar[s], m0 + 64 * i, kk);
+          }
+          if (!sh.b_mn) {
+            ptx::tma_load_2d(sb, tb, &full_bar[s], kk, n0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kBlockN / 64; ++i)
+              ptx::tma_load_2d(sb + i * kMnBoxBytes, tb, &full_bar[s], n0 + 64 * i, kk);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc_bf16(kBlockM, kBlockN, sh.a_mn, sh.b_mn);
+      // K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart; a k-step of 16
+      // elements advances the start address by 32 bytes inside the swizzle span.
+      // MN-major tile: boxes of 64 (mn) x 64 (k); 8-k groups 1024 bytes apart (SBO),
+      // 64-wide mn groups one box (8192 bytes) apart (LBO); a k-step advances by 16 rows.
+      const uint32_t a_lbo = sh.a_mn ? kMnBoxBytes : 0, a_step = sh.a_mn ? kUmmaK * 128 : kUmmaK * 2;
+      const uint32_t b_lbo = sh.b_mn ? kMnBoxBytes : 0, b_step = sh.b_mn ? kUmmaK * 128 : kUmmaK * 2;
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1u;
+        const uint32_t aph = (tcount >> 1) & 1u;
+        if (!ptx::mbar_wait(&tempty_bar[acc], aph ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(sh.status, 0, (kDevTimeoutMma << 24) | 0x800000 | (tcount & 0x7FFFFF));
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(sh.status, 0, (kDevTimeoutMma << 24) | (it & 0x7FFFFF));
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_base = ptx::smem_u32(smem + s * kStageBytes);
+          const uint32_t b_base = a_base + kTileABytes;
+#pragma unroll
+          for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
+            const uint64_t da = ptx::make_smem_desc_sw128(a_base + ks * a_step, a_lbo, 1024);
+            const uint64_t db = ptx::make_smem_desc_sw128(b_base + ks * b_step, b_lbo, 1024);
+            ptx::umma_bf16_ss(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[s]);   // frees the smem stage once these MMAs have read it
+        }
+        if (ok) ptx::umma_commit(&tfull_bar[acc]);   // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = warp & 3;   // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+      const uint32_t acc = tcount & 1u;
+      const uint32_t aph = (tcount >> 1) & 1u;
+      const int m0 = (tile / sh.tiles_n) * kBlockM;
+      const int n0 = (tile % sh.tiles_n) * kBlockN;
+      if (!ptx::mbar_wait(&tfull_bar[acc], aph, abort_flag)) {
+        *abort_flag = 1;
+        atomicCAS(sh.status, 0, (kDevTimeoutEpilogue << 24) | (tcount & 0xFFFFFF));
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBlockN;
+#pragma unroll 1
+      for (int c = 0; c < kBlockN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= sh.n) break;
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(t_row + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (row < sh.m) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          epi(row, col0, v);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  // ------------------------------ tear-down ------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // give copies that may still be in flight time to land before shared memory is released
+    for (int i = 0; i < 2000; ++i) __nanosleep(200);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace moc
