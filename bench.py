@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the MoC sparse SwiGLU FFN hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ffn-type moc|moc_gcp|moc_2_8]
+
+Workload (N = 1 and every rank of N > 1): one MoC FFN layer at the 1b-preset shape
+(d=2048, d_ffn=5461, K=1024), bf16, X [8, 2048, 2048] = 16 384 tokens per GPU, forward +
+backward with an upstream gradient; a "step" is one such pass. Weights ~N(0, 0.02) (same on all
+ranks), X and dY ~N(0, 1) (per-rank seed): seeded synthetic data with the shapes and
+distributions of the reference's single-layer training benchmark
+(benchmarks/training/benchmark_training_latency.py:20-22, :112-124). With N > 1 the tokens are
+sharded (each rank runs its own 16 384), weight gradients are averaged with NCCL, overlapped
+with the rest of the backward pass; weak scaling.
+
+Prints one JSON line (rank 0). `value`: tokens/s of the whole job with inputs resident in HBM,
+CUDA-event timed, max over ranks. `e2e`: the same through the public module API with HOST
+(pinned) inputs: every step copies X and dY to the device and Y and dX back. `roofline`: the
+tcgen05 GEMM kernel (all dense contractions of the step), timed live with events recorded
+between the kernels of the timed steps. `cpu_baseline` / `--impl reference`: the CPU oracle
+(restatement of the reference's PyTorch path) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+D, D_FFN, K_SEL = 2048, 5461, 1024
+TOKENS = 8 * 2048
+METRIC = "moc_ffn_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+CPU_SAMPLE_TOKENS = 1024
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8"])
+    ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_config(args, world):
+    return {
+        "workload": f"configs[1]: single MoC FFN layer fwd+bwd, 1b preset d={D} d_ffn={D_FFN} K={K_SEL}, "
+                    f"X[8,2048,{D}] bf16, ffn_type={args.ffn_type}",
+        "tokens_per_gpu": args.tokens,
+        "global_tokens": args.tokens * world,
+        "parallelism": f"token-sharded dp{world}" if world > 1 else "single GPU",
+        "l2": "inputs larger than L2: every step streams >600 MB of activations, weights and scratch "
+              "(126 MB L2), no explicit flush",
+    }
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU oracle leg (cpu_baseline and --impl reference)
+# ----------------------------------------------------------------------------------------------
+
+
+def cpu_oracle_step_fn(ffn_type):
+    import torch
+    from oracle import moc_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    x, dy, wg, wu, wd = O.make_inputs(CPU_SAMPLE_TOKENS, D, D_FFN, torch.bfloat16, seed=1234)
+    select = "2of8" if ffn_type == "moc_2_8" else "topk"
+
+    def step():
+        fwd = O.moc_forward(x, wg, wu, wd, K_SEL, select=select)
+        if ffn_type == "moc_gcp":
+            O.moc_backward(dy, x, wg, wu, wd, fwd["idx"], fwd["g_sel"], fwd["u_sel"])
+        else:
+            O.moc_backward(dy, x, wg, wu, wd, fwd["idx"], fwd["g_sel"], fwd["u_sel"], fwd["s_sel"], fwd["z_sel"])
+
+    return step, torch.get_num_threads()
+
+
+def cpu_baseline(ffn_type, budget_s=12.0):
+    step, threads = cpu_oracle_step_fn(ffn_type)
+    step()
+    n, t0 = 0, time.perf_counter()
+    while True:
+        step()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s and n >= 2 or n >= 200:
+            break
+    return {
+        "value": CPU_SAMPLE_TOKENS * n / dt,
+        "unit": UNIT,
+        "cores": threads,
+        "kind": "port",
+        "sample": f"{n} fwd+bwd passes of the CPU oracle over {CPU_SAMPLE_TOKENS} tokens of the same shape (bf16), "
+                  f"{dt:.1f} s",
+    }
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    step, threads = cpu_oracle_step_fn(args.ffn_type)
+    for _ in range(max(1, args.warmup)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = CPU_SAMPLE_TOKENS * args.steps / dt
+    cfg = workload_config(args, world)
+    sample = (f"each step = one fwd+bwd pass of the CPU oracle over a {CPU_SAMPLE_TOKENS}-token sample of the "
+              f"workload (bf16), {threads} host threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": cfg,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU leg
+# ----------------------------------------------------------------------------------------------
+
+
+class ClockSampler:
+    """Samples nvidia-smi every 50 ms in the background; stop(t0, t1) keeps the samples whose
+    timestamps fall inside the wall-clock window [t0, t1] (the timed region)."""
+
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self, t0, t1):
+        import datetime
+
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
+        for line in out.strip().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), float(f[3]),
+                             [n for n, v in zip(names, f[5:9]) if v.lower().startswith("active")]))
+            except ValueError:
+                continue
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        note = "samples inside the timed region"
+        if not inside:       # region shorter than the sampling period: fall back to the busiest samples
+            inside = sorted(rows, key=lambda r: -r[3])[:3]
+            note = "timed region shorter than the sampling period: the 3 highest-power samples around it"
+        sm = sorted(r[1] for r in inside)
+        reasons = sorted({n for r in inside for n in r[4]})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max((r[2] for r in inside), default=None),
+                "power_w_max": max((r[3] for r in inside), default=None), "samples": len(inside),
+                "reasons": reasons, "note": note}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return d, "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import moc_b200
+    from moc_b200 import _lib
+    from moc_b200.dp import GradAllReducer
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()   # raises if the CUDA library is missing
+
+    tokens = args.tokens
+    gw = torch.Generator().manual_seed(0)
+    module = moc_b200.build_ffn(D, D_FFN, args.ffn_type, k=K_SEL)
+    with torch.no_grad():
+        for p in module.parameters():
+            p.copy_(torch.randn(p.shape, generator=gw) * 0.02)
+    module = module.to(device=dev, dtype=torch.bfloat16).train()
+    gx = torch.Generator().manual_seed(1234 + rank)
+    x_host = torch.randn(8, tokens // 8, D, generator=gx).bfloat16().pin_memory()
+    dy_host = torch.randn(8, tokens // 8, D, generator=gx).bfloat16().pin_memory()
+    x = x_host.to(dev).requires_grad_(True)
+    dy = dy_host.to(dev)
+    reducer = GradAllReducer(average=True) if world > 1 else None
+
+    def step(xin, dyin):
+        module.zero_grad(set_to_none=True)
+        xin.grad = None
+        y = module(xin)
+        if reducer is not None:
+            with reducer:
+                y.backward(dyin)
+        else:
+            y.backward(dyin)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    moc_b200.set_status_checks(True)    # one checked step: raises if a device-side wait timed out
+    step(x, dy)
+    moc_b200.set_status_checks(False)
+    for _ in range(max(3, args.warmup)):
+        step(x, dy)
+    barrier()
+
+    # ---- timed region: K steps, HBM-resident inputs, per-kernel events between launches ----
+    cap = min(4096, 16 * args.steps + 16)
+    prof_events = [torch.cuda.Event(enable_timing=True) for _ in range(cap)]
+    for ev in prof_events:
+        ev.record()    # forces creation of the underlying cudaEvent_t
+    torch.cuda.synchronize()
+    handles = (ctypes.c_void_p * cap)(*[ev.cuda_event for ev in prof_events])
+    tags = (ctypes.c_int * cap)()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    _lib.check(lib.moc_profile_begin(handles, cap), "moc_profile_begin")
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    wall0 = time.perf_counter()
+    epoch0 = time.time()
+    t_start.record()
+    for _ in range(args.steps):
+        step(x, dy)
+    t_end.record()
+    torch.cuda.synchronize()
+    n_prof = lib.moc_profile_end(tags, cap)
+    barrier()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop(epoch0, epoch0 + wall) if rank == 0 else None
+    ms_total = t_start.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+
+    # per-kernel durations from the event profile
+    kinds = {1: "gemm_tcgen05", 2: "gemm_simt", 3: "topk_select", 4: "select_2of8", 5: "expand_z", 6: "transpose"}
+    per_kind = {}
+    launches = 0
+    for i in range(min(n_prof, cap) - 1):
+        tag = tags[i]
+        if tag == 0:
+            continue
+        launches += 1
+        dur = prof_events[i].elapsed_time(prof_events[i + 1])
+        name = kinds.get(tag, f"tag{tag}")
+        tot, cnt = per_kind.get(name, (0.0, 0))
+        per_kind[name] = (tot + dur, cnt + 1)
+    if n_prof and tags[min(n_prof, cap) - 1] != 0:
+        launches += 1
+    peaks, peak_src = load_peaks()
+    gemm_ms, gemm_n = per_kind.get("gemm_tcgen05", (0.0, 0))
+    flops_per_step = 18.0 * tokens * D * D_FFN
+    k_eff = K_SEL
+    roofline = None
+    if gemm_n:
+        achieved = flops_per_step * args.steps / (gemm_ms * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        roofline = {
+            "bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": achieved, "peak": peak,
+            "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_src} (sustained cuBLAS bf16)",
+            "launches": gemm_n, "avg_launch_ms": gemm_ms / gemm_n,
+            "algorithmic_flops_per_step": flops_per_step, "traffic": None,
+        }
+    kernel_share = {name: {"ms_per_step": tot / args.steps, "launches_per_step": cnt / args.steps}
+                    for name, (tot, cnt) in sorted(per_kind.items())}
+
+    # ---- e2e: host (pinned) inputs in, host outputs back, every step ----
+    e2e = None
+    if not args.no_e2e:
+        y_host = torch.empty_like(x_host)
+        dx_host = torch.empty_like(x_host)
+        x_dev = torch.empty_like(x).requires_grad_(True)
+        dy_dev = torch.empty_like(dy)
+
+        def e2e_step():
+            with torch.no_grad():
+                x_dev.copy_(x_host, non_blocking=True)
+                dy_dev.copy_(dy_host, non_blocking=True)
+            y = step(x_dev, dy_dev)
+            y_host.copy_(y.detach(), non_blocking=True)
+            dx_host.copy_(x_dev.grad, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        e_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        nbytes = x_host.numel() * 2
+        e2e = {"value": tokens * world * args.steps / (e_ms * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": 2 * nbytes,
+               "ms_per_step": e_ms / args.steps,
+               "what": "module(x).backward(dy) with x, dy copied from pinned host memory and y, dx copied back, "
+                       "each step"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(args.ffn_type)
+
+    if rank == 0:
+        value = tokens * world * args.steps / (ms_total * 1e-3)
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args, world), "e2e": e2e, "gpu_launches": launches,
+            "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "kernels": kernel_share,
+            "host_wall_ms_per_step": 1e3 * wall / args.steps, "k_selected": k_eff,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1 and args.gpus > 1:
+        # launched without torchrun: re-exec under torch.distributed.run
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29531"),
+               str(Path(__file__).resolve())] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -117,6 +117,18 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
                 void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
                 int64_t workspace_bytes, void* ev_down, void* ev_gate, void* ev_up, void* stream);
 
+/* Per-kernel timing without a profiler. Between moc_profile_begin and moc_profile_end (process-wide,
+ * one profile at a time) the library records events[0], events[1], ... (a HOST array of created
+ * cudaEvent_t handles, timing enabled) on the stream of each call, one right before every
+ * kernel it launches and one when an FFN entry point returns. moc_profile_end copies the
+ * kernel-kind tag of each recorded event to tags_out and returns their number; the time
+ * between events i and i+1 is the duration of kernel i. Tags: 0 end of call, 1 tcgen05 GEMM,
+ * 2 CUDA-core GEMM, 3 Top-K select, 4 2:8 select, 5 expand, 6 transpose, 7-11 decode kernels.
+ * No counterpart in the reference, which times whole passes with CUDA events
+ * (benchmarks/training/benchmark_training_latency.py:59-106). */
+int moc_profile_begin(void** events, int capacity);
+int moc_profile_end(int* tags_out, int capacity);
+
 /* Synchronises `stream` and returns MOC_OK, or MOC_ERR_DEVICE_TIMEOUT if a kernel of the
  * last call that used `workspace` recorded a bounded-wait failure in its status area. */
 int moc_read_status(const void* workspace, void* stream);

@@ -8,7 +8,8 @@
 #include "internal.h"
 
 namespace moc {
-const char* last_error_text();
+void profile_begin(cudaEvent_t* events, int capacity);
+int profile_end(int* tags_out, int capacity);
 }
 
 using namespace moc;
@@ -220,7 +221,9 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   q.b0 = operand(w_down_t, d, 1);
   q.epi = store_epi(y, d, 0);
   q.status = status;
-  return launch_gemm(q, stream);
+  rc = launch_gemm(q, stream);
+  prof_mark(kProfEnd, stream);
+  return rc;
 }
 
 int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* grad_y, const void* x,
@@ -328,8 +331,21 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   gx.a1 = operand(buf_b, ld, 0);
   gx.b1 = operand(w_up, d, 1);
   gx.epi = store_epi(grad_x, d, 0);
-  return launch_gemm(gx, stream);
+  rc = launch_gemm(gx, stream);
+  prof_mark(kProfEnd, stream);
+  return rc;
 }
+
+int moc_profile_begin(void** events, int capacity) {
+  if (!events || capacity <= 0) {
+    set_error("moc_profile_begin: need a host array of cudaEvent_t handles");
+    return kErrInvalidArg;
+  }
+  profile_begin(reinterpret_cast<cudaEvent_t*>(events), capacity);
+  return kOk;
+}
+
+int moc_profile_end(int* tags_out, int capacity) { return profile_end(tags_out, capacity); }
 
 int moc_read_status(const void* workspace, void* stream_) {
   if (!workspace) {

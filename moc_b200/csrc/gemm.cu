@@ -38,6 +38,43 @@ int check_last(const char* what) {
   return kOk;
 }
 
+// ---- optional per-kernel event profile ---------------------------------------------------------
+struct Profile {
+  cudaEvent_t* events = nullptr;
+  int capacity = 0;
+  int count = 0;
+  int tags[4096];
+};
+// process-wide (PyTorch runs backward passes on its own autograd threads)
+static Profile g_prof;
+static std::mutex g_prof_mutex;
+
+void prof_mark(int tag, cudaStream_t stream) {
+  if (!g_prof.events) return;
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  if (!g_prof.events || g_prof.count >= g_prof.capacity || g_prof.count >= 4096) return;
+  if (cudaEventRecord(g_prof.events[g_prof.count], stream) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  g_prof.tags[g_prof.count++] = tag;
+}
+void profile_begin(cudaEvent_t* events, int capacity) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_prof.events = events;
+  g_prof.capacity = capacity;
+  g_prof.count = 0;
+}
+int profile_end(int* tags_out, int capacity) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  const int n = g_prof.count;
+  for (int i = 0; i < n && i < capacity; ++i) tags_out[i] = g_prof.tags[i];
+  g_prof.events = nullptr;
+  g_prof.capacity = 0;
+  g_prof.count = 0;
+  return n;
+}
+
 // ---- driver entry point for tensor-map encoding (no link-time dependency on libcuda) -----------
 static PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -133,14 +170,11 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
   sh.tiles_n = ceil_div_i(p.n, kBlockN);
   sh.status = p.status;
   auto kern = gemm_tcgen05_kernel<Epi>;
-  static thread_local const void* configured = nullptr;
-  if (configured != reinterpret_cast<const void*>(kern)) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) != cudaSuccess)
-      return check_last("gemm smem attribute");
-    configured = reinterpret_cast<const void*>(kern);
-  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) != cudaSuccess)
+    return check_last("gemm smem attribute");
   const int tiles = sh.tiles_m * sh.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
+  prof_mark(kProfGemmTc, stream);
   kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ta0, tb0, ta1, tb1, sh, epi);
   return check_last("gemm_tcgen05");
 }
@@ -160,6 +194,7 @@ static int launch_simt(const GemmProblem& p, const Epi& epi, cudaStream_t stream
   SimtOperand<T> a0 = simt_operand<T>(p.a0), b0 = simt_operand<T>(p.b0);
   SimtOperand<T> a1 = p.k1 > 0 ? simt_operand<T>(p.a1) : a0;
   SimtOperand<T> b1 = p.k1 > 0 ? simt_operand<T>(p.b1) : b0;
+  prof_mark(kProfGemmSimt, stream);
   gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(a0, b0, p.k0, a1, b1, p.k1 > 0 ? p.k1 : 0, p.m, p.n,
                                                               epi);
   return check_last("gemm_simt");

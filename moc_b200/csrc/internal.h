@@ -62,6 +62,17 @@ int launch_expand_z(int dtype, const uint32_t* bitmap, const uint16_t* rank0, co
 int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_t ld_out, int rows, int cols,
                      cudaStream_t stream);
 
+// Optional per-kernel timing: while a profile is active (moc_profile_begin), every launcher
+// records the next caller-provided event right before its kernel launch, tagged with the
+// kernel kind; API entry points add an end marker. Intervals between consecutive events on
+// one stream are the kernels' durations.
+enum ProfTag : int {
+  kProfEnd = 0, kProfGemmTc = 1, kProfGemmSimt = 2, kProfTopk = 3, kProfSel2of8 = 4, kProfExpand = 5,
+  kProfTranspose = 6, kProfDecodeGate = 7, kProfDecodeUp = 8, kProfDecodeDown = 9, kProfDecodeFused28 = 10,
+  kProfDecodeDense = 11,
+};
+void prof_mark(int tag, cudaStream_t stream);
+
 int check_last(const char* what);
 const char* last_error_text();
 void set_error(const char* fmt, ...);

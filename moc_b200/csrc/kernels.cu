@@ -316,6 +316,7 @@ static int topk_select_t(const void* g, int64_t ldg, int tokens, int d_ffn, int 
           cudaSuccess)                                                                                           \
         return check_last("topk_select smem attribute");                                                         \
     }                                                                                                            \
+    prof_mark(kProfTopk, stream);                                                                                \
     kern<<<tokens, kSelThreads, smem, stream>>>(gp, ldg, d_ffn, k, words, idx, gs, bitmap, rank0);               \
   } while (0)
   if (chunk <= 8) MOC_SEL_LAUNCH(8);
@@ -343,6 +344,7 @@ int launch_select_2of8(int dtype, const void* g, int64_t ldg, int tokens, int d_
   const int64_t total = static_cast<int64_t>(tokens) * words;
   const int threads = 128;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  prof_mark(kProfSel2of8, stream);
   if (dtype == kBF16)
     select_2of8_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(g), ldg, tokens, d_ffn, k_eff, words, idx,
@@ -361,6 +363,7 @@ int launch_expand_z(int dtype, const uint32_t* bitmap, const uint16_t* rank0, co
   const int64_t total = static_cast<int64_t>(tokens) * words;
   const int threads = 128;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  prof_mark(kProfExpand, stream);
   if (dtype == kBF16)
     expand_z_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
         bitmap, rank0, static_cast<const __nv_bfloat16*>(z_sel), static_cast<const __nv_bfloat16*>(g_sel),
@@ -378,6 +381,7 @@ int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_
   if (rows == 0 || cols == 0) return kOk;
   const dim3 block(32, 8);
   const dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+  prof_mark(kProfTranspose, stream);
   if (dtype == kBF16)
     transpose_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), ld_in,
                                                                 static_cast<__nv_bfloat16*>(out), ld_out, rows, cols);

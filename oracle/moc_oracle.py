@@ -112,16 +112,24 @@ def _select(g, k, select):
     raise ValueError(select)
 
 
-def moc_forward(x, gate_w, up_w, down_w, k, select="topk"):
+def moc_forward(x, gate_w, up_w, down_w, k, select="topk", idx_override=None):
     """MoC forward, pure-PyTorch branch of the reference (moc/ffn.py:141-163 for `moc`,
     :389-414 for `moc_gcp`, :277-298 for `moc_2_8`). All tensors share one dtype (fp32 or
     bf16); every op rounds to that dtype exactly where the reference's tensor ops do.
 
-    Returns a dict: y, idx (int64, ascending), g_sel, u_sel, s_sel, z_sel.
+    ``idx_override`` (int64 [..., k]) replaces the selection step by a given channel set; the
+    tests use it to compare the remaining arithmetic under an identical mask when the gate
+    values of two implementations differ in their last bit.
+
+    Returns a dict: y, idx (int64, ascending), g_sel, u_sel, s_sel, z_sel, g (dense gate).
     """
     inter = gate_w.shape[0]
     g = x @ gate_w.t()                                   # ffn.py:141
-    g_sel, idx = _select(g, k, select)                   # ffn.py:144
+    if idx_override is None:
+        g_sel, idx = _select(g, k, select)               # ffn.py:144
+    else:
+        idx = idx_override
+        g_sel = torch.gather(g, -1, idx)
     u = x @ up_w.t()                                     # ffn.py:146
     u_sel = torch.gather(u, -1, idx)                     # ffn.py:156
     s_sel = F.silu(g_sel)                                # ffn.py:157
@@ -129,7 +137,7 @@ def moc_forward(x, gate_w, up_w, down_w, k, select="topk"):
     z_full = torch.zeros(*x.shape[:-1], inter, dtype=z_sel.dtype)
     z_full.scatter_(-1, idx, z_sel)                      # ffn.py:160-161
     y = z_full @ down_w.t()                              # ffn.py:163
-    return dict(y=y, idx=idx, g_sel=g_sel, u_sel=u_sel, s_sel=s_sel, z_sel=z_sel)
+    return dict(y=y, idx=idx, g_sel=g_sel, u_sel=u_sel, s_sel=s_sel, z_sel=z_sel, g=g)
 
 
 def moc_backward(grad_y, x, gate_w, up_w, down_w, idx, g_sel, u_sel, s_sel=None, z_sel=None):
