@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8"])
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
+    ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -319,6 +320,13 @@ def run_ours(args, rank, world, local_rank):
         }
     kernel_share = {name: {"ms_per_step": tot / args.steps, "launches_per_step": cnt / args.steps}
                     for name, (tot, cnt) in sorted(per_kind.items())}
+    if args.dump_kernels and rank == 0:
+        # launch-by-launch durations of the last timed step, in launch order
+        n = min(n_prof, cap)
+        per_step = max(1, n // max(1, args.steps))
+        seq = [(kinds.get(tags[i], "end"), round(prof_events[i].elapsed_time(prof_events[i + 1]), 4))
+               for i in range(max(0, n - per_step), n - 1)]
+        print("last step, launch order:", seq, file=sys.stderr, flush=True)
 
     # ---- e2e: host (pinned) inputs in, host outputs back, every step ----
     e2e = None

@@ -209,5 +209,5 @@ def test_full_size_properties():
     sel = torch.zeros(tokens, d_ffn, dtype=torch.bool, device="cuda").scatter_(1, idx, True)
     lo_sel = torch.where(sel, g.float(), torch.full_like(g.float(), float("inf"))).min(dim=1).values
     hi_unsel = torch.where(sel, torch.full_like(g.float(), float("-inf")), g.float()).max(dim=1).values
-    # gates from two GEMM implementations differ by at most one bf16 ulp
-    assert (lo_sel >= hi_unsel - 2 ** -7 * hi_unsel.abs()).all()
+    # gates from two GEMM implementations can each be off by one bf16 ulp, in opposite directions
+    assert (lo_sel >= hi_unsel - 2 ** -6 * hi_unsel.abs()).all()
