@@ -105,15 +105,17 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
 
 /* MoC FFN backward. Replaces _MoCFunction.backward / _MoCGCPFunction.backward
  * (moc/ffn.py:176-259, :424-497) including scatter_sparse_to_dense and sparse_backward_aux
- * (moc/training/triton_sparse_aux.py:266-423). s_sel / z_sel NULL = recompute them from
- * g_sel, u_sel (moc_gcp). Outputs are overwritten, not accumulated: grad_x[tokens, d],
+ * (moc/training/triton_sparse_aux.py:266-423). idx, g_sel, u_sel [tokens, k] are the forward
+ * pass's outputs (the compact saved set, moc/ffn.py:166-169, :417). z_sel NULL = recompute it
+ * from g_sel, u_sel (moc_gcp, moc/ffn.py:435-436); s_sel is accepted for symmetry and not read
+ * (s = SiLU(g_sel) is rebuilt with the same bits). Outputs are overwritten, not accumulated: grad_x[tokens, d],
  * grad_w_gate[d_ffn, d], grad_w_up[d_ffn, d], grad_w_down[d, d_ffn] (parameter layout).
  * ev_down / ev_gate / ev_up: optional cudaEvent_t handles recorded on `stream` as soon as the
  * respective weight gradient is final, so a caller can start its all-reduce while the rest of
  * the backward pass runs. */
 int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* grad_y, const void* x,
-                const void* w_gate, const void* w_up, const void* w_down_t, const uint32_t* bitmap,
-                const uint16_t* rank0, const void* g_sel, const void* u_sel, const void* s_sel, const void* z_sel,
+                const void* w_gate, const void* w_up, const void* w_down_t, const int16_t* idx,
+                const void* g_sel, const void* u_sel, const void* s_sel, const void* z_sel,
                 void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
                 int64_t workspace_bytes, void* ev_down, void* ev_gate, void* ev_up, void* stream);
 

@@ -35,7 +35,7 @@ SIGNATURES = {
     "moc_gemm": (c_int, [c_int, c_int, c_int64, c_int64, c_int64, _P, c_int64, c_int, _P, c_int64, c_int, _P,
                          c_int64, c_int, _P, _P]),
     "moc_ffn_fwd": (c_int, [c_int, c_int, c_int64, c_int64, c_int64, c_int64] + [_P] * 13 + [c_int64, _P]),
-    "moc_ffn_bwd": (c_int, [c_int, c_int64, c_int64, c_int64, c_int64] + [_P] * 16 + [c_int64, _P, _P, _P, _P]),
+    "moc_ffn_bwd": (c_int, [c_int, c_int64, c_int64, c_int64, c_int64] + [_P] * 15 + [c_int64, _P, _P, _P, _P]),
     "moc_profile_begin": (c_int, [_P, c_int]),
     "moc_profile_end": (c_int, [_P, c_int]),
     "moc_read_status": (c_int, [_P, _P]),

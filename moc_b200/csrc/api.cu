@@ -55,10 +55,21 @@ MatOperand operand(const void* p, int64_t ld, int mn_major) {
 EpiArgs store_epi(void* c, int64_t ldc, int transposed) {
   EpiArgs e = {};
   e.kind = kEpiStore;
-  e.c = c;
-  e.ldc = ldc;
-  e.transposed = transposed;
+  e.c[0] = c;
+  e.ldc[0] = ldc;
+  e.transposed[0] = transposed;
   return e;
+}
+
+GemmProblem problem(int dtype, int* status, int64_t m, int64_t n, int64_t k) {
+  GemmProblem p = {};
+  p.dtype = dtype;
+  p.status = status;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.k0 = (int)k;
+  p.groups = 1;
+  return p;
 }
 
 int record(void* ev, cudaStream_t stream) {
@@ -83,7 +94,7 @@ int64_t moc_ffn_fwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
   return kStatusBytes + round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
 }
 int64_t moc_ffn_bwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
-  return kStatusBytes + 2 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
+  return kStatusBytes + 3 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
 }
 
 int moc_transpose(int dtype, const void* in, void* out, int64_t rows, int64_t cols, void* stream) {
@@ -104,8 +115,8 @@ int moc_topk_select(int dtype, const void* g, int64_t ldg, int64_t tokens, int64
     set_error("moc_topk_select: null pointer or ldg < d_ffn");
     return kErrInvalidArg;
   }
-  return launch_topk_select(dtype, g, ldg, (int)tokens, (int)d_ffn, (int)k, idx, g_sel, bitmap, rank0,
-                            as_stream(stream));
+  return launch_topk_select(dtype, const_cast<void*>(g), ldg, (int)tokens, (int)d_ffn, (int)k, 0, idx, g_sel, bitmap,
+                            rank0, as_stream(stream));
 }
 
 int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64_t d_ffn, int16_t* idx, void* g_sel,
@@ -117,7 +128,8 @@ int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64
     set_error("moc_select_2of8: null pointer or ldg < d_ffn");
     return kErrInvalidArg;
   }
-  return launch_select_2of8(dtype, g, ldg, (int)tokens, (int)d_ffn, idx, g_sel, bitmap, rank0, as_stream(stream));
+  return launch_select_2of8(dtype, const_cast<void*>(g), ldg, (int)tokens, (int)d_ffn, 0, idx, g_sel, bitmap, rank0,
+                            as_stream(stream));
 }
 
 int moc_gemm(int dtype, int impl, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_mn,
@@ -129,17 +141,11 @@ int moc_gemm(int dtype, int impl, int64_t m, int64_t n, int64_t k, const void* a
     set_error("moc_gemm: bad sizes or null pointer");
     return kErrInvalidArg;
   }
-  GemmProblem p = {};
-  p.dtype = dtype;
+  GemmProblem p = problem(dtype, status, m, n, k);
   p.impl = impl;
-  p.m = (int)m;
-  p.n = (int)n;
-  p.k0 = (int)k;
-  p.a0 = operand(a, lda, a_mn);
-  p.b0 = operand(b, ldb, b_mn);
-  p.k1 = 0;
+  p.a[0] = operand(a, lda, a_mn);
+  p.b[0] = operand(b, ldb, b_mn);
   p.epi = store_epi(c, ldc, c_transposed);
-  p.status = status;
   return launch_gemm(p, as_stream(stream));
 }
 
@@ -178,26 +184,21 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   const int words = (int)mask_words(d_ffn);
 
   // G = X Wg^T (moc/ffn.py:141), rounded to the storage type, rows padded to ld
-  GemmProblem p = {};
-  p.dtype = dtype;
-  p.m = (int)tokens;
-  p.n = (int)d_ffn;
-  p.k0 = (int)d;
-  p.a0 = operand(x, d, 0);
-  p.b0 = operand(w_gate, d, 0);
+  GemmProblem p = problem(dtype, status, tokens, d_ffn, d);
+  p.a[0] = operand(x, d, 0);
+  p.b[0] = operand(w_gate, d, 0);
   p.epi = store_epi(dense, ld, 0);
-  p.status = status;
   if ((rc = launch_gemm(p, stream)) != kOk) return rc;
 
-  // channel selection on the rounded G (moc/ffn.py:144-147)
+  // channel selection on the rounded G (moc/ffn.py:144-147); G becomes S' = mask * SiLU(G) (moc/ffn.py:157)
   if (select == MOC_SELECT_TOPK)
-    rc = launch_topk_select(dtype, dense, ld, (int)tokens, (int)d_ffn, (int)k, idx, g_sel, bitmap, rank0, stream);
+    rc = launch_topk_select(dtype, dense, ld, (int)tokens, (int)d_ffn, (int)k, 1, idx, g_sel, bitmap, rank0, stream);
   else
-    rc = launch_select_2of8(dtype, dense, ld, (int)tokens, (int)d_ffn, idx, g_sel, bitmap, rank0, stream);
+    rc = launch_select_2of8(dtype, dense, ld, (int)tokens, (int)d_ffn, 1, idx, g_sel, bitmap, rank0, stream);
   if (rc != kOk) return rc;
 
-  // U = X Wu^T with the selected-activation epilogue; G is overwritten by Z' (moc/ffn.py:146-161)
-  p.b0 = operand(w_up, d, 0);
+  // U = X Wu^T with the selected-activation epilogue; S' is overwritten by Z' (moc/ffn.py:146-161)
+  p.b[0] = operand(w_up, d, 0);
   p.epi = EpiArgs{};
   p.epi.kind = kEpiUpSparse;
   p.epi.dense0 = dense;
@@ -212,29 +213,24 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   if ((rc = launch_gemm(p, stream)) != kOk) return rc;
 
   // Y = Z' Wd^T (moc/ffn.py:163): A = Z' [tokens, F] K-major, B = W_down^T [F, d] N-contiguous
-  GemmProblem q = {};
-  q.dtype = dtype;
-  q.m = (int)tokens;
-  q.n = (int)d;
-  q.k0 = (int)d_ffn;
-  q.a0 = operand(dense, ld, 0);
-  q.b0 = operand(w_down_t, d, 1);
+  GemmProblem q = problem(dtype, status, tokens, d, d_ffn);
+  q.a[0] = operand(dense, ld, 0);
+  q.b[0] = operand(w_down_t, d, 1);
   q.epi = store_epi(y, d, 0);
-  q.status = status;
   rc = launch_gemm(q, stream);
   prof_mark(kProfEnd, stream);
   return rc;
 }
 
 int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, const void* grad_y, const void* x,
-                const void* w_gate, const void* w_up, const void* w_down_t, const uint32_t* bitmap,
-                const uint16_t* rank0, const void* g_sel, const void* u_sel, const void* s_sel, const void* z_sel,
+                const void* w_gate, const void* w_up, const void* w_down_t, const int16_t* idx,
+                const void* g_sel, const void* u_sel, const void* s_sel, const void* z_sel,
                 void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
                 int64_t workspace_bytes, void* ev_down, void* ev_gate, void* ev_up, void* stream_) {
   if (bad_dtype(dtype)) return kErrInvalidArg;
   int rc = check_dims(tokens, d, d_ffn, k);
   if (rc != kOk) return rc;
-  if (!grad_y || !x || !w_gate || !w_up || !w_down_t || !bitmap || !rank0 || !g_sel || !u_sel || !grad_x ||
+  if (!grad_y || !x || !w_gate || !w_up || !w_down_t || !idx || !g_sel || !u_sel || !grad_x ||
       !grad_w_gate || !grad_w_up || !grad_w_down || !workspace) {
     set_error("moc_ffn_bwd: null pointer");
     return kErrInvalidArg;
@@ -245,6 +241,7 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
               (long long)workspace_bytes, (long long)moc_ffn_bwd_workspace_bytes(dtype, tokens, d_ffn));
     return kErrWorkspace;
   }
+  (void)s_sel;   // s = round(SiLU(g)) is recomputed; the saved copy holds the same bits
   cudaStream_t stream = as_stream(stream_);
   int* status = static_cast<int*>(workspace);
   if (cudaMemsetAsync(status, 0, kStatusBytes, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
@@ -261,75 +258,60 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
     return kOk;
   }
   const int64_t ld = ffn_ld(d_ffn);
-  const int words = (int)mask_words(d_ffn);
   const int64_t dense_bytes = round_up_i64(tokens * ld * (int64_t)es, 256);
-  void* buf_a = static_cast<uint8_t*>(workspace) + kStatusBytes;
-  void* buf_b = static_cast<uint8_t*>(buf_a) + dense_bytes;
+  void* buf_z = static_cast<uint8_t*>(workspace) + kStatusBytes;     // Z'
+  void* buf_u = static_cast<uint8_t*>(buf_z) + dense_bytes;          // dZ, then dU'
+  void* buf_g = static_cast<uint8_t*>(buf_u) + dense_bytes;          // dG'
 
   // Z' from the saved (or recomputed) selected activations (moc/ffn.py:196-199, :435-442)
-  if ((rc = launch_expand_z(dtype, bitmap, rank0, z_sel, g_sel, u_sel, buf_a, ld, (int)tokens, (int)d_ffn, (int)k,
+  if ((rc = launch_expand_z(dtype, idx, z_sel, g_sel, u_sel, buf_z, ld, (int)tokens, (int)d_ffn, (int)k,
                             stream)) != kOk)
     return rc;
 
-  // dW_down[d, F] = dY^T Z' (moc/ffn.py:203), computed as the [F, d] product Z'^T dY and
-  // stored transposed so that warps write along the channel dimension.
-  GemmProblem p = {};
-  p.dtype = dtype;
-  p.status = status;
-  p.m = (int)d_ffn;
-  p.n = (int)d;
-  p.k0 = (int)tokens;
-  p.a0 = operand(buf_a, ld, 1);
-  p.b0 = operand(grad_y, d, 1);
-  p.epi = store_epi(grad_w_down, d_ffn, 1);
-  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
-  if ((rc = record(ev_down, stream)) != kOk) return rc;
-
-  // dZ = dY W_down (moc/ffn.py:206) with the gather + SiLU' epilogue -> dense dG', dU' (moc/ffn.py:209-237)
-  GemmProblem z = {};
-  z.dtype = dtype;
-  z.status = status;
-  z.m = (int)tokens;
-  z.n = (int)d_ffn;
-  z.k0 = (int)d;
-  z.a0 = operand(grad_y, d, 0);
-  z.b0 = operand(w_down_t, d, 0);
-  z.epi.kind = kEpiBwdSparse;
-  z.epi.dense0 = buf_a;
-  z.epi.dense1 = buf_b;
-  z.epi.ld_dense = ld;
-  z.epi.bitmap = bitmap;
-  z.epi.rank0 = rank0;
-  z.epi.words = words;
-  z.epi.k_sel = (int)k;
-  z.epi.g_sel = g_sel;
-  z.epi.u_sel = const_cast<void*>(u_sel);
-  z.epi.s_sel = const_cast<void*>(s_sel);
+  // dZ = dY W_down (moc/ffn.py:206), rounded to the storage type
+  GemmProblem z = problem(dtype, status, tokens, d_ffn, d);
+  z.a[0] = operand(grad_y, d, 0);
+  z.b[0] = operand(w_down_t, d, 0);
+  z.epi = store_epi(buf_u, ld, 0);
   if ((rc = launch_gemm(z, stream)) != kOk) return rc;
 
-  // dW_gate = dG'^T X, dW_up = dU'^T X (moc/ffn.py:239-253)
-  p.epi = store_epi(grad_w_gate, d, 0);
-  p.a0 = operand(buf_a, ld, 1);
-  p.b0 = operand(x, d, 1);
-  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
-  if ((rc = record(ev_gate, stream)) != kOk) return rc;
-  p.epi = store_epi(grad_w_up, d, 0);
-  p.a0 = operand(buf_b, ld, 1);
-  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
-  if ((rc = record(ev_up, stream)) != kOk) return rc;
+  // gather through the mask, SiLU', zero fill -> dense dG', dU' (moc/ffn.py:209-237)
+  if ((rc = launch_bwd_sparse(dtype, idx, g_sel, u_sel, buf_u, buf_g, ld, (int)tokens, (int)d_ffn, (int)k,
+                              stream)) != kOk)
+    return rc;
+
+  // The three weight gradients in one grouped launch, each an [F, d] product over the tokens:
+  //   dW_down[d, F] = dY^T Z'  (moc/ffn.py:203)  computed as Z'^T dY and stored transposed,
+  //   dW_gate[F, d] = dG'^T X, dW_up[F, d] = dU'^T X  (moc/ffn.py:239-253).
+  GemmProblem w = problem(dtype, status, d_ffn, d, tokens);
+  w.groups = 3;
+  w.a[0] = operand(buf_z, ld, 1);
+  w.b[0] = operand(grad_y, d, 1);
+  w.a[1] = operand(buf_g, ld, 1);
+  w.b[1] = operand(x, d, 1);
+  w.a[2] = operand(buf_u, ld, 1);
+  w.b[2] = operand(x, d, 1);
+  w.epi = EpiArgs{};
+  w.epi.kind = kEpiStore;
+  w.epi.c[0] = grad_w_down;
+  w.epi.ldc[0] = d_ffn;
+  w.epi.transposed[0] = 1;
+  w.epi.c[1] = grad_w_gate;
+  w.epi.ldc[1] = d;
+  w.epi.c[2] = grad_w_up;
+  w.epi.ldc[2] = d;
+  if ((rc = launch_gemm(w, stream)) != kOk) return rc;
+  if ((rc = record(ev_down, stream)) != kOk || (rc = record(ev_gate, stream)) != kOk ||
+      (rc = record(ev_up, stream)) != kOk)
+    return rc;
 
   // dX = dG' W_gate + dU' W_up (moc/ffn.py:245-255), one accumulator over two K segments
-  GemmProblem gx = {};
-  gx.dtype = dtype;
-  gx.status = status;
-  gx.m = (int)tokens;
-  gx.n = (int)d;
-  gx.k0 = (int)d_ffn;
-  gx.a0 = operand(buf_a, ld, 0);
-  gx.b0 = operand(w_gate, d, 1);
+  GemmProblem gx = problem(dtype, status, tokens, d, d_ffn);
   gx.k1 = (int)d_ffn;
-  gx.a1 = operand(buf_b, ld, 0);
-  gx.b1 = operand(w_up, d, 1);
+  gx.a[0] = operand(buf_g, ld, 0);
+  gx.b[0] = operand(w_gate, d, 1);
+  gx.a[1] = operand(buf_u, ld, 0);
+  gx.b[1] = operand(w_up, d, 1);
   gx.epi = store_epi(grad_x, d, 0);
   rc = launch_gemm(gx, stream);
   prof_mark(kProfEnd, stream);

@@ -49,29 +49,40 @@ template <> struct Num<float> {
   __device__ __forceinline__ static float round(float v) { return v; }
 };
 
-// SiLU evaluated in fp32: g * sigmoid(g) (moc/training/triton_sparse_aux.py:39).
-// Full-precision expf (not __expf): the results are compared with PyTorch's.
-__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
-__device__ __forceinline__ float sigmoid_f32(float g) { return 1.0f / (1.0f + expf(-g)); }
+// Sigmoid evaluated in fp32 (SiLU(g) = g * sigmoid(g), moc/training/triton_sparse_aux.py:39).
+// fp32 tensors: full-precision expf and IEEE division. bf16 tensors: ex2/rcp approximations
+// (about 2 fp32 ulp), far below the bf16 rounding that follows; the same function is used
+// wherever a value is recomputed, so forward and backward agree bit for bit.
+template <typename T> __device__ __forceinline__ float sigmoid_act(float g);
+template <> __device__ __forceinline__ float sigmoid_act<float>(float g) { return 1.0f / (1.0f + expf(-g)); }
+template <> __device__ __forceinline__ float sigmoid_act<__nv_bfloat16>(float g) {
+  return __fdividef(1.0f, 1.0f + __expf(-g));
+}
+
+// s = round(SiLU(g)) (moc/ffn.py:157)
+template <typename T>
+__device__ __forceinline__ float silu_round(float g) { return Num<T>::round(g * sigmoid_act<T>(g)); }
 
 // Selected-channel forward math: s = round(SiLU(g)), z = round(s * u)
 // (moc/training/triton_sparse_aux.py:39-45).
 template <typename T>
 __device__ __forceinline__ void moc_fwd_point(float g, float u, float& s, float& z) {
-  s = Num<T>::round(silu_f32(g));
+  s = silu_round<T>(g);
   z = Num<T>::round(s * u);
 }
 
 // Selected-channel backward math (moc/ffn.py:222-229 via
 // moc/training/triton_sparse_aux.py:376-400): with storage type bf16 every step of
 // SiLU' is rounded, as the chain of PyTorch bf16 ops does; in fp32 nothing is.
+// s = round(SiLU(g)) is rebuilt from the same sigmoid evaluation.
 template <typename T>
-__device__ __forceinline__ void moc_bwd_point(float g, float u, float s, float gz,
-                                              float& grad_g, float& grad_u) {
+__device__ __forceinline__ void moc_bwd_point(float g, float u, float gz, float& grad_g, float& grad_u) {
   using N = Num<T>;
+  const float sig_full = sigmoid_act<T>(g);
+  const float s = N::round(g * sig_full);
   const float grad_s = N::round(u * gz);
   grad_u = N::round(s * gz);
-  const float sig = N::round(sigmoid_f32(g));
+  const float sig = N::round(sig_full);
   const float one_minus = N::round(1.0f - sig);
   const float g_term = N::round(g * one_minus);
   const float inner = N::round(1.0f + g_term);
@@ -94,7 +105,7 @@ __host__ __device__ __forceinline__ int ceil_div_i(int a, int b) { return (a + b
 
 // Leading dimension (elements) of the dense [tokens, d_ffn] scratch matrices: rows
 // start on 128-byte boundaries and 32-column chunks never cross the row end.
-__host__ __device__ __forceinline__ int64_t ffn_ld(int64_t d_ffn) { return round_up_i64(d_ffn, 64); }
+__host__ __device__ __forceinline__ int64_t ffn_ld(int64_t d_ffn) { return round_up_i64(d_ffn, 128); }
 // 32-bit words per row of the selection bitmap.
 __host__ __device__ __forceinline__ int64_t mask_words(int64_t d_ffn) { return ffn_ld(d_ffn) / 32; }
 

@@ -1,34 +1,49 @@
-// Epilogue functors shared by the tcgen05 GEMM core (bf16) and the SIMT GEMM core
-// (fp32). A functor is called by one thread with one output row and 32 consecutive
-// columns [col0, col0 + 32), col0 % 32 == 0, row < M, col0 < N; acc[j] is the fp32
-// accumulator of column col0 + j (zero for columns >= N).
+// Epilogue functors shared by the tcgen05 GEMM core (bf16) and the CUDA-core GEMM core
+// (fp32). One thread owns one output row and walks a run of 32-column chunks of it:
 //
-// The sparse epilogues are where the MoC-specific work is fused into the GEMMs; they
-// replace the gather / scatter helper kernels of the reference
-// (moc/training/triton_sparse_aux.py:17-182) and never write a full U or dZ to HBM.
+//   Ctx ctx;                                         per-thread state for the run
+//   epi.begin(ctx, group, row, col_first, nchunks);  issue loads needed by the whole run
+//   for c in [0, nchunks):  col0 = col_first + 32 * c
+//     epi.prefetch(ctx, row, col0, c);               issue global loads of chunk c (the
+//                                                    accumulator load is still in flight)
+//     epi(ctx, group, row, col0, c, acc);            acc[j] = fp32 accumulator of column col0 + j
+//
+// with col0 % 32 == 0, row < M, col0 < N, nchunks <= 4, and acc zero for columns >= N.
+// `group` is the problem index of a grouped launch (0 otherwise).
+//
+// The sparse forward epilogue is where the MoC-specific work is fused into the up-projection
+// GEMM; it replaces sparse_forward_aux of the reference
+// (moc/training/triton_sparse_aux.py:17-49, :197-231) and never writes a full U to HBM.
 #pragma once
 
 #include "common.cuh"
 
 namespace moc {
 
+constexpr int kMaxGroups = 3;
+constexpr int kEpiMaxChunks = 4;
+
 // ---- 32-element row-chunk load / store ------------------------------------------------
 template <typename T> struct Chunk32;
 
 template <> struct Chunk32<__nv_bfloat16> {
-  // p must be 16-byte aligned
-  __device__ __forceinline__ static void load(const __nv_bfloat16* p, float (&v)[32]) {
-    const uint4* q = reinterpret_cast<const uint4*>(p);
+  static constexpr int kVecs = 4;   // 16-byte vectors per chunk
+  __device__ __forceinline__ static void unpack(const uint4 (&q)[4], float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 w = q[i];
-      const uint32_t a[4] = {w.x, w.y, w.z, w.w};
+      const uint32_t a[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         v[i * 8 + 2 * j] = __uint_as_float(a[j] << 16);
         v[i * 8 + 2 * j + 1] = __uint_as_float(a[j] & 0xFFFF0000u);
       }
     }
+  }
+  // p must be 16-byte aligned
+  __device__ __forceinline__ static void load_raw(const __nv_bfloat16* p, uint4 (&q)[4]) {
+    const uint4* s = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = s[i];
   }
   __device__ __forceinline__ static void store(__nv_bfloat16* p, const float (&v)[32]) {
     uint4* q = reinterpret_cast<uint4*>(p);
@@ -46,13 +61,20 @@ template <> struct Chunk32<__nv_bfloat16> {
 };
 
 template <> struct Chunk32<float> {
-  __device__ __forceinline__ static void load(const float* p, float (&v)[32]) {
-    const float4* q = reinterpret_cast<const float4*>(p);
+  static constexpr int kVecs = 8;
+  __device__ __forceinline__ static void unpack(const uint4 (&q)[8], float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float4 w = q[i];
-      v[4 * i] = w.x; v[4 * i + 1] = w.y; v[4 * i + 2] = w.z; v[4 * i + 3] = w.w;
+      v[4 * i] = __uint_as_float(q[i].x);
+      v[4 * i + 1] = __uint_as_float(q[i].y);
+      v[4 * i + 2] = __uint_as_float(q[i].z);
+      v[4 * i + 3] = __uint_as_float(q[i].w);
     }
+  }
+  __device__ __forceinline__ static void load_raw(const float* p, uint4 (&q)[8]) {
+    const uint4* s = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = s[i];
   }
   __device__ __forceinline__ static void store(float* p, const float (&v)[32]) {
     float4* q = reinterpret_cast<float4*>(p);
@@ -61,26 +83,38 @@ template <> struct Chunk32<float> {
   }
 };
 
-// ---- plain store: C[row, col] (or C[col, row] when transposed) --------------------------
+template <typename T>
+__device__ __forceinline__ void chunk_load(const T* p, float (&v)[32]) {
+  uint4 q[Chunk32<T>::kVecs];
+  Chunk32<T>::load_raw(p, q);
+  Chunk32<T>::unpack(q, v);
+}
+
+// ---- plain store: C[row, col] (or C[col, row] when transposed), one C per group ------------
 template <typename T>
 struct EpiStore {
-  T* c;
-  int64_t ldc;
-  int n;            // valid columns
-  int transposed;   // 1: write C[col * ldc + row]
-  int vec_ok;       // 1: rows of C are 16-byte aligned at every col0 (checked on the host)
+  struct Ctx {};
+  T* c[kMaxGroups];
+  int64_t ldc[kMaxGroups];
+  int transposed[kMaxGroups];   // 1: write C[col * ldc + row]
+  int vec_ok[kMaxGroups];       // 1: rows of C are 16-byte aligned at every col0 (checked on the host)
+  int n;                        // valid columns
 
-  __device__ __forceinline__ void operator()(int row, int col0, const float (&acc)[32]) const {
+  __device__ __forceinline__ void begin(Ctx&, int, int, int, int) const {}
+  __device__ __forceinline__ void prefetch(Ctx&, int, int, int) const {}
+  __device__ __forceinline__ void operator()(Ctx&, int group, int row, int col0, int, const float (&acc)[32]) const {
     const int ncols = min(32, n - col0);
-    if (transposed) {
-      T* p = c + static_cast<int64_t>(col0) * ldc + row;
+    T* base = c[group];
+    const int64_t ld = ldc[group];
+    if (transposed[group]) {
+      T* p = base + static_cast<int64_t>(col0) * ld + row;
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (j < ncols) p[static_cast<int64_t>(j) * ldc] = Num<T>::from_float(acc[j]);
+        if (j < ncols) p[static_cast<int64_t>(j) * ld] = Num<T>::from_float(acc[j]);
       return;
     }
-    T* p = c + static_cast<int64_t>(row) * ldc + col0;
-    if (vec_ok && ncols == 32) {
+    T* p = base + static_cast<int64_t>(row) * ld + col0;
+    if (vec_ok[group] && ncols == 32) {
       Chunk32<T>::store(p, acc);
     } else {
 #pragma unroll
@@ -91,16 +125,24 @@ struct EpiStore {
 };
 
 // ---- forward: up projection -> selected activations -------------------------------------
-// acc = U tile. For every selected channel (bit set in the row's bitmap) computes
-// u = round(U), s = round(SiLU(g)), z = round(s * u) (moc/ffn.py:156-158), writes them
-// to the compact per-token arrays at the channel's rank, and overwrites the dense G
-// chunk in place with the zero-filled Z' chunk that the down projection consumes
-// (moc/ffn.py:160-163).
+// acc = U tile. The selection kernel has already replaced the dense gate row by
+// S' = mask * round(SiLU(G)) (zero outside the selected channels, moc/ffn.py:157), so the
+// epilogue is branch-free dense math: u = round(U), z = round(S' * u) (moc/ffn.py:158),
+// written over the S' chunk in place as the zero-filled Z' chunk that the down projection
+// consumes (moc/ffn.py:160-163). The selected u (and on request s, z) also go to the
+// compact per-token arrays at the channel's rank (moc/ffn.py:156, :166-169). Mask words and
+// ranks of the whole run are fetched in begin(); the S' chunk is fetched in prefetch(),
+// while the accumulator load is in flight.
 template <typename T>
 struct EpiUpSparse {
-  T* gz;                    // in: G [tokens, ld]; out: Z' [tokens, ld]
+  struct Ctx {
+    uint32_t word[kEpiMaxChunks];
+    uint32_t rank[kEpiMaxChunks];
+    uint4 s[Chunk32<T>::kVecs];
+  };
+  T* sz;                    // in: S' [tokens, ld]; out: Z' [tokens, ld]
   int64_t ld;
-  const uint32_t* bitmap;   // [tokens, words]
+  const uint32_t* bitmap;   // [tokens, words], words % 4 == 0
   const uint16_t* rank0;    // [tokens, words] rank of the first channel of each word
   int words;
   int k;
@@ -108,106 +150,78 @@ struct EpiUpSparse {
   T* s_sel;                 // [tokens, k] or null
   T* z_sel;                 // [tokens, k] or null
 
-  __device__ __forceinline__ void operator()(int row, int col0, const float (&acc)[32]) const {
-    const int w = col0 >> 5;
-    const uint32_t word = bitmap[static_cast<int64_t>(row) * words + w];
-    T* chunk = gz + static_cast<int64_t>(row) * ld + col0;
-    float out[32];
-    if (word == 0u) {
+  __device__ __forceinline__ void begin(Ctx& ctx, int, int row, int col_first, int nchunks) const {
+    const int w0 = col_first >> 5;
+    const uint32_t* bw = bitmap + static_cast<int64_t>(row) * words + w0;
+    const uint16_t* rk = rank0 + static_cast<int64_t>(row) * words + w0;
+    if ((w0 & 3) == 0) {   // aligned run of four words: one 16-byte and one 8-byte load
+      const uint4 b = *reinterpret_cast<const uint4*>(bw);
+      const uint2 r = *reinterpret_cast<const uint2*>(rk);
+      ctx.word[0] = b.x; ctx.word[1] = b.y; ctx.word[2] = b.z; ctx.word[3] = b.w;
+      ctx.rank[0] = r.x & 0xFFFFu; ctx.rank[1] = r.x >> 16; ctx.rank[2] = r.y & 0xFFFFu; ctx.rank[3] = r.y >> 16;
+    } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) out[j] = 0.0f;
-      Chunk32<T>::store(chunk, out);
-      return;
+      for (int c = 0; c < kEpiMaxChunks; ++c) {
+        ctx.word[c] = (c < nchunks) ? bw[c] : 0u;
+        ctx.rank[c] = (c < nchunks) ? rk[c] : 0u;
+      }
     }
-    float g[32];
-    Chunk32<T>::load(chunk, g);
-    const int base = rank0[static_cast<int64_t>(row) * words + w];
-    const int64_t crow = static_cast<int64_t>(row) * k;
+  }
+  __device__ __forceinline__ void prefetch(Ctx& ctx, int row, int col0, int c) const {
+    if (ctx.word[c] != 0u) Chunk32<T>::load_raw(sz + static_cast<int64_t>(row) * ld + col0, ctx.s);
+  }
+  __device__ __forceinline__ void operator()(Ctx& ctx, int, int row, int col0, int c, const float (&acc)[32]) const {
+    const uint32_t word = ctx.word[c];
+    T* chunk = sz + static_cast<int64_t>(row) * ld + col0;
+    if (word == 0u) return;   // the S' chunk is all zero already and stays the Z' chunk
+    float s[32], out[32];
+    Chunk32<T>::unpack(ctx.s, s);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = Num<T>::round(s[j] * Num<T>::round(acc[j]));
+    Chunk32<T>::store(chunk, out);
+    T* up = u_sel + static_cast<int64_t>(row) * k + ctx.rank[c];
+    T* sp = s_sel ? s_sel + static_cast<int64_t>(row) * k + ctx.rank[c] : nullptr;
+    T* zp = z_sel ? z_sel + static_cast<int64_t>(row) * k + ctx.rank[c] : nullptr;
+    int pos = 0;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      out[j] = 0.0f;
       if ((word >> j) & 1u) {
-        const int pos = base + __popc(word & ((1u << j) - 1u));
-        const float u = Num<T>::round(acc[j]);
-        float s, z;
-        moc_fwd_point<T>(g[j], u, s, z);
-        u_sel[crow + pos] = Num<T>::from_float(u);
-        if (s_sel) s_sel[crow + pos] = Num<T>::from_float(s);
-        if (z_sel) z_sel[crow + pos] = Num<T>::from_float(z);
-        out[j] = z;
+        up[pos] = Num<T>::from_float(acc[j]);
+        if (sp) sp[pos] = Num<T>::from_float(s[j]);
+        if (zp) zp[pos] = Num<T>::from_float(out[j]);
+        ++pos;
       }
     }
-    Chunk32<T>::store(chunk, out);
-  }
-};
-
-// ---- backward: dZ = dY * W_down -> dense zero-filled dG', dU' ---------------------------
-// acc = dZ tile. For every selected channel: gz = round(dZ), grad_s = round(u * gz),
-// grad_u = round(s * gz), grad_g = round(grad_s * SiLU'(g)) with SiLU' rounded step by
-// step as the reference does (moc/ffn.py:219-237, moc/training/triton_sparse_aux.py:376-400).
-// With s_sel == null (moc_gcp) s is recomputed from g (moc/ffn.py:435).
-template <typename T>
-struct EpiBwdSparse {
-  T* grad_g;                // [tokens, ld] dense out
-  T* grad_u;                // [tokens, ld] dense out
-  int64_t ld;
-  const uint32_t* bitmap;
-  const uint16_t* rank0;
-  int words;
-  int k;
-  const T* g_sel;
-  const T* u_sel;
-  const T* s_sel;           // null -> recompute
-
-  __device__ __forceinline__ void operator()(int row, int col0, const float (&acc)[32]) const {
-    const int w = col0 >> 5;
-    const uint32_t word = bitmap[static_cast<int64_t>(row) * words + w];
-    T* pg = grad_g + static_cast<int64_t>(row) * ld + col0;
-    T* pu = grad_u + static_cast<int64_t>(row) * ld + col0;
-    float og[32], ou[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) { og[j] = 0.0f; ou[j] = 0.0f; }
-    if (word != 0u) {
-      const int base = rank0[static_cast<int64_t>(row) * words + w];
-      const int64_t crow = static_cast<int64_t>(row) * k;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        if ((word >> j) & 1u) {
-          const int pos = base + __popc(word & ((1u << j) - 1u));
-          const float g = Num<T>::to_float(g_sel[crow + pos]);
-          const float u = Num<T>::to_float(u_sel[crow + pos]);
-          const float s = s_sel ? Num<T>::to_float(s_sel[crow + pos]) : Num<T>::round(silu_f32(g));
-          const float gz = Num<T>::round(acc[j]);
-          moc_bwd_point<T>(g, u, s, gz, og[j], ou[j]);
-        }
-      }
-    }
-    Chunk32<T>::store(pg, og);
-    Chunk32<T>::store(pu, ou);
   }
 };
 
 // ---- dense SwiGLU forward: acc = U tile, Z = round(round(SiLU(G)) * round(U)) ------------
-// (moc/ffn.py:120-121). Overwrites G in place with Z and keeps U for the backward pass.
+// (moc/ffn.py:120-121). Reads G, writes U (kept for the backward pass) and Z.
 template <typename T>
 struct EpiDenseSwiGLU {
-  T* gz;       // in: G, out: Z
-  T* u_out;    // U (saved for backward) or null
+  struct Ctx {
+    uint4 g[Chunk32<T>::kVecs];
+  };
+  const T* g;   // [tokens, ld]
+  T* u_out;     // [tokens, ld]
+  T* z_out;     // [tokens, ld]
   int64_t ld;
 
-  __device__ __forceinline__ void operator()(int row, int col0, const float (&acc)[32]) const {
-    T* chunk = gz + static_cast<int64_t>(row) * ld + col0;
-    float g[32], out[32], u[32];
-    Chunk32<T>::load(chunk, g);
+  __device__ __forceinline__ void begin(Ctx&, int, int, int, int) const {}
+  __device__ __forceinline__ void prefetch(Ctx& ctx, int row, int col0, int) const {
+    Chunk32<T>::load_raw(g + static_cast<int64_t>(row) * ld + col0, ctx.g);
+  }
+  __device__ __forceinline__ void operator()(Ctx& ctx, int, int row, int col0, int, const float (&acc)[32]) const {
+    float gv[32], out[32], u[32];
+    Chunk32<T>::unpack(ctx.g, gv);
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       u[j] = Num<T>::round(acc[j]);
-      float s, z;
-      moc_fwd_point<T>(g[j], u[j], s, z);
-      out[j] = z;
+      float s;
+      moc_fwd_point<T>(gv[j], u[j], s, out[j]);
     }
-    if (u_out) Chunk32<T>::store(u_out + static_cast<int64_t>(row) * ld + col0, u);
-    Chunk32<T>::store(chunk, out);
+    Chunk32<T>::store(u_out + static_cast<int64_t>(row) * ld + col0, u);
+    Chunk32<T>::store(z_out + static_cast<int64_t>(row) * ld + col0, out);
   }
 };
 

@@ -144,38 +144,37 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
     set_error("tcgen05 GEMM needs a device status word");
     return kErrInvalidArg;
   }
-  CUtensorMap ta0, tb0, ta1, tb1;
+  GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const int nmaps = p.k1 > 0 ? 2 : p.groups;
   int rc;
-  if ((rc = make_operand_map(&ta0, p.a0, p.m, p.k0, kBlockM)) != kOk) return rc;
-  if ((rc = make_operand_map(&tb0, p.b0, p.n, p.k0, kBlockN)) != kOk) return rc;
-  if (p.k1 > 0) {
-    if ((rc = make_operand_map(&ta1, p.a1, p.m, p.k1, kBlockM)) != kOk) return rc;
-    if ((rc = make_operand_map(&tb1, p.b1, p.n, p.k1, kBlockN)) != kOk) return rc;
-    if (p.a1.mn_major != p.a0.mn_major || p.b1.mn_major != p.b0.mn_major) {
-      set_error("both K segments must use the same operand majors");
+  for (int i = 0; i < nmaps; ++i) {
+    const int kext = (p.k1 > 0 && i == 1) ? p.k1 : p.k0;
+    if ((rc = make_operand_map(&maps.a[i], p.a[i], p.m, kext, kBlockM)) != kOk) return rc;
+    if ((rc = make_operand_map(&maps.b[i], p.b[i], p.n, kext, kBlockN)) != kOk) return rc;
+    if (p.a[i].mn_major != p.a[0].mn_major || p.b[i].mn_major != p.b[0].mn_major) {
+      set_error("all K segments / groups of one launch must use the same operand majors");
       return kErrUnsupported;
     }
-  } else {
-    ta1 = ta0;
-    tb1 = tb0;
   }
   GemmShape sh;
   sh.m = p.m;
   sh.n = p.n;
   sh.kb0 = ceil_div_i(p.k0, kBlockK);
   sh.kb1 = p.k1 > 0 ? ceil_div_i(p.k1, kBlockK) : 0;
-  sh.a_mn = p.a0.mn_major;
-  sh.b_mn = p.b0.mn_major;
+  sh.groups = p.groups;
+  sh.a_mn = p.a[0].mn_major;
+  sh.b_mn = p.b[0].mn_major;
   sh.tiles_m = ceil_div_i(p.m, kBlockM);
   sh.tiles_n = ceil_div_i(p.n, kBlockN);
   sh.status = p.status;
   auto kern = gemm_tcgen05_kernel<Epi>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) != cudaSuccess)
     return check_last("gemm smem attribute");
-  const int tiles = sh.tiles_m * sh.tiles_n;
+  const int tiles = sh.tiles_m * sh.tiles_n * sh.groups;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   prof_mark(kProfGemmTc, stream);
-  kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(ta0, tb0, ta1, tb1, sh, epi);
+  kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(maps, sh, epi);
   return check_last("gemm_tcgen05");
 }
 
@@ -191,23 +190,26 @@ static SimtOperand<T> simt_operand(const MatOperand& op) {
 template <typename T, class Epi>
 static int launch_simt(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
   const dim3 grid(ceil_div_i(p.n, kSimtBN), ceil_div_i(p.m, kSimtBM));
-  SimtOperand<T> a0 = simt_operand<T>(p.a0), b0 = simt_operand<T>(p.b0);
-  SimtOperand<T> a1 = p.k1 > 0 ? simt_operand<T>(p.a1) : a0;
-  SimtOperand<T> b1 = p.k1 > 0 ? simt_operand<T>(p.b1) : b0;
-  prof_mark(kProfGemmSimt, stream);
-  gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(a0, b0, p.k0, a1, b1, p.k1 > 0 ? p.k1 : 0, p.m, p.n,
-                                                              epi);
-  return check_last("gemm_simt");
+  for (int g = 0; g < p.groups; ++g) {
+    SimtOperand<T> a0 = simt_operand<T>(p.a[g]), b0 = simt_operand<T>(p.b[g]);
+    SimtOperand<T> a1 = p.k1 > 0 ? simt_operand<T>(p.a[1]) : a0;
+    SimtOperand<T> b1 = p.k1 > 0 ? simt_operand<T>(p.b[1]) : b0;
+    prof_mark(kProfGemmSimt, stream);
+    gemm_simt_kernel<T, Epi><<<grid, kSimtThreads, 0, stream>>>(a0, b0, p.k0, a1, b1, p.k1 > 0 ? p.k1 : 0, p.m, p.n, g,
+                                                                epi);
+    const int rc = check_last("gemm_simt");
+    if (rc != kOk) return rc;
+  }
+  return kOk;
 }
-
-template <typename T, class Epi>
-static int launch_core(const GemmProblem& p, const Epi& epi, cudaStream_t stream);
 
 template <class Epi>
 static int launch_core_bf16(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
   if (p.impl == 1) return launch_simt<__nv_bfloat16, Epi>(p, epi, stream);
   return launch_tcgen05<Epi>(p, epi, stream);
 }
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T>
 static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
@@ -217,28 +219,33 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
     if constexpr (Num<T>::kIsBf16) return launch_core_bf16<E>(p, epi, stream);
     else return launch_simt<T, E>(p, epi, stream);
   };
-  const bool dense_aligned = (reinterpret_cast<uintptr_t>(e.dense0) & 15u) == 0 &&
-                             (reinterpret_cast<uintptr_t>(e.dense1) & 15u) == 0 && e.ld_dense % 64 == 0;
+  const bool dense_ok = aligned16(e.dense0) && aligned16(e.dense1) && aligned16(e.dense2) && e.ld_dense % 128 == 0;
   switch (e.kind) {
     case kEpiStore: {
       EpiStore<T> epi;
-      epi.c = static_cast<T*>(e.c);
-      epi.ldc = e.ldc;
+      for (int g = 0; g < kMaxGroups; ++g) {
+        const int s = g < p.groups ? g : 0;
+        epi.c[g] = static_cast<T*>(e.c[s]);
+        epi.ldc[g] = e.ldc[s];
+        epi.transposed[g] = e.transposed[s];
+        epi.vec_ok[g] = (!e.transposed[s] && aligned16(e.c[s]) &&
+                         (e.ldc[s] * static_cast<int64_t>(sizeof(T))) % 16 == 0) ? 1 : 0;
+        if (g < p.groups && !e.c[s]) {
+          set_error("GEMM output pointer of group %d is null", g);
+          return kErrInvalidArg;
+        }
+      }
       epi.n = p.n;
-      epi.transposed = e.transposed;
-      epi.vec_ok = (!e.transposed && (reinterpret_cast<uintptr_t>(e.c) & 15u) == 0 &&
-                    (e.ldc * static_cast<int64_t>(sizeof(T))) % 16 == 0)
-                       ? 1
-                       : 0;
       return run(epi);
     }
     case kEpiUpSparse: {
-      if (!dense_aligned) {
-        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 64");
+      if (!dense_ok || e.words % 4 != 0 || !aligned16(e.bitmap) || (reinterpret_cast<uintptr_t>(e.rank0) & 7u)) {
+        set_error("dense scratch / mask arrays must be 16-byte aligned with a leading dimension that is a "
+                  "multiple of 128");
         return kErrWorkspace;
       }
       EpiUpSparse<T> epi;
-      epi.gz = static_cast<T*>(e.dense0);
+      epi.sz = static_cast<T*>(e.dense0);
       epi.ld = e.ld_dense;
       epi.bitmap = e.bitmap;
       epi.rank0 = e.rank0;
@@ -249,32 +256,15 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
       epi.z_sel = static_cast<T*>(e.z_sel);
       return run(epi);
     }
-    case kEpiBwdSparse: {
-      if (!dense_aligned) {
-        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 64");
-        return kErrWorkspace;
-      }
-      EpiBwdSparse<T> epi;
-      epi.grad_g = static_cast<T*>(e.dense0);
-      epi.grad_u = static_cast<T*>(e.dense1);
-      epi.ld = e.ld_dense;
-      epi.bitmap = e.bitmap;
-      epi.rank0 = e.rank0;
-      epi.words = e.words;
-      epi.k = e.k_sel;
-      epi.g_sel = static_cast<const T*>(e.g_sel);
-      epi.u_sel = static_cast<const T*>(e.u_sel);
-      epi.s_sel = static_cast<const T*>(e.s_sel);
-      return run(epi);
-    }
     case kEpiDenseSwiGLU: {
-      if (!dense_aligned) {
-        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 64");
+      if (!dense_ok) {
+        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 128");
         return kErrWorkspace;
       }
       EpiDenseSwiGLU<T> epi;
-      epi.gz = static_cast<T*>(e.dense0);
+      epi.g = static_cast<const T*>(e.dense0);
       epi.u_out = static_cast<T*>(e.dense1);
+      epi.z_out = static_cast<T*>(e.dense2);
       epi.ld = e.ld_dense;
       return run(epi);
     }
@@ -286,7 +276,11 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
 
 int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
   if (p.m <= 0 || p.n <= 0) return kOk;
-  if (p.k0 <= 0 || !p.a0.ptr || !p.b0.ptr) {
+  if (p.groups < 1 || p.groups > kGemmMaxGroups || (p.groups > 1 && p.k1 > 0)) {
+    set_error("GEMM: groups must be 1..%d and exclude a second K segment", kGemmMaxGroups);
+    return kErrInvalidArg;
+  }
+  if (p.k0 <= 0 || !p.a[0].ptr || !p.b[0].ptr) {
     set_error("GEMM needs K >= 1 and non-null operands");
     return kErrInvalidArg;
   }

@@ -6,6 +6,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "epilogues.cuh"
 
 namespace moc {
 
@@ -52,7 +53,7 @@ __device__ __forceinline__ void simt_load_tile(const SimtOperand<T>& op, int mn0
 template <typename T, class Epi>
 __global__ void __launch_bounds__(kSimtThreads)
 gemm_simt_kernel(SimtOperand<T> a0, SimtOperand<T> b0, int k0_len, SimtOperand<T> a1, SimtOperand<T> b1, int k1_len,
-                 int m, int n, const Epi epi) {
+                 int m, int n, int group, const Epi epi) {
   __shared__ __align__(16) float as[kSimtBK][kSimtBM + 4];
   __shared__ __align__(16) float bs[kSimtBK][kSimtBN + 4];
   const int m0 = blockIdx.y * kSimtBM;
@@ -87,7 +88,12 @@ gemm_simt_kernel(SimtOperand<T> a0, SimtOperand<T> b0, int k0_len, SimtOperand<T
     }
   }
   const int row = m0 + r, col0 = n0 + h;
-  if (row < m && col0 < n) epi(row, col0, acc);
+  if (row < m && col0 < n) {
+    typename Epi::Ctx ctx;
+    epi.begin(ctx, group, row, col0, 1);
+    epi.prefetch(ctx, row, col0, 0);
+    epi(ctx, group, row, col0, 0, acc);
+  }
 }
 
 }  // namespace moc

@@ -1,16 +1,20 @@
-// bf16 GEMM core for sm_100a: C[M,N] = sum over up to two K segments of A_s[M,K_s] * B_s[N,K_s]^T,
-// fp32 accumulation in tensor memory, fused epilogue functor.
+// bf16 GEMM core for sm_100a: C[M,N] = A[M,K] * B[N,K]^T, fp32 accumulation in tensor memory,
+// fused epilogue functor.
 //
 //   * persistent: one CTA per SM walks output tiles of 128 x 256;
 //   * warp 0 = TMA producer (4-stage ring of 128-byte-swizzled A/B tiles, BLOCK_K = 64),
 //     warp 1 = tcgen05.mma issuer (one elected thread; also owns the TMEM allocation),
-//     warps 2-5 = epilogue (each reads its 32-lane TMEM quadrant with tcgen05.ld);
+//     warps 2-9 = epilogue: two warps per 32-lane TMEM quadrant, each taking one 128-column
+//     half of the tile, so that global-memory latency in a fused epilogue is covered by a
+//     second warp on the same scheduler;
 //   * two 256-column TMEM accumulators, so the epilogue of tile i overlaps the MMAs of
 //     tile i + 1;
 //   * both operands may be K-major (K contiguous in memory) or MN-major (M/N contiguous),
 //     which covers X*W^T, dY*W and the dW = act^T * X products without any transposed copy;
-//   * the optional second K segment accumulates a second product into the same tile
+//   * two K segments may accumulate two products into the same tile
 //     (dX = dG'*W_gate + dU'*W_up, moc/ffn.py:245-255) before the epilogue runs;
+//   * up to three same-shape problems may share one launch ("groups": the three dW products
+//     of the backward pass), which removes most of the wave-quantisation tail;
 //   * every mbarrier wait is bounded: on a time-out the kernel records a code in the
 //     status word, all roles leave their loops, TMEM is released and the kernel returns.
 //
@@ -21,6 +25,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "epilogues.cuh"
 #include "ptx.cuh"
 
 namespace moc {
@@ -35,12 +40,21 @@ constexpr int kTileBBytes = kBlockN * kBlockK * 2;   // 32 KiB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kMnBoxBytes = 64 * kBlockK * 2;        // one MN-major TMA box: 64 (mn) x 64 (k)
 constexpr int kTmemCols = 512;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
+// Operand descriptors of one launch: (a[i], b[i]) is K segment i of a two-segment product, or
+// problem i of a grouped launch.
+struct GemmMaps {
+  CUtensorMap a[kMaxGroups];
+  CUtensorMap b[kMaxGroups];
+};
+
 struct GemmShape {
-  int m, n;          // extents of C
+  int m, n;          // extents of C (of every group)
   int kb0, kb1;      // number of 64-wide k-blocks in segment 0 / 1 (kb1 == 0: single product)
+  int groups;        // >= 1; groups > 1 requires kb1 == 0
   int a_mn, b_mn;    // 1 = operand is MN-major in memory
   int tiles_m, tiles_n;
   int* status;       // device status word
@@ -48,9 +62,7 @@ struct GemmShape {
 
 template <class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_b0,
-                    const __grid_constant__ CUtensorMap tm_a1, const __grid_constant__ CUtensorMap tm_b1,
-                    const GemmShape sh, const Epi epi) {
+gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, const Epi epi) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -63,15 +75,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = sh.tiles_m * sh.tiles_n;
+  const int tiles_per_group = sh.tiles_m * sh.tiles_n;
+  const int num_tiles = tiles_per_group * sh.groups;
   const int kb_total = sh.kb0 + sh.kb1;
 
   if (threadIdx.x == 0) {
-    ptx::prefetch_tensormap(&tm_a0);
-    ptx::prefetch_tensormap(&tm_b0);
-    if (sh.kb1 > 0) {
-      ptx::prefetch_tensormap(&tm_a1);
-      ptx::prefetch_tensormap(&tm_b1);
+    const int nmaps = sh.kb1 > 0 ? 2 : sh.groups;
+    for (int i = 0; i < nmaps; ++i) {
+      ptx::prefetch_tensormap(&maps.a[i]);
+      ptx::prefetch_tensormap(&maps.b[i]);
     }
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
@@ -80,8 +92,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_cons
     }
     ptx::mbar_init(&tfull_bar[0], 1);
     ptx::mbar_init(&tfull_bar[1], 1);
-    ptx::mbar_init(&tempty_bar[0], 128);
-    ptx::mbar_init(&tempty_bar[1], 128);
+    ptx::mbar_init(&tempty_bar[0], 32 * kEpiWarps);
+    ptx::mbar_init(&tempty_bar[1], 32 * kEpiWarps);
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -101,8 +113,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_cons
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / sh.tiles_n) * kBlockM;
-        const int n0 = (tile % sh.tiles_n) * kBlockN;
+        const int group = tile / tiles_per_group;
+        const int t = tile - group * tiles_per_group;
+        const int m0 = (t / sh.tiles_n) * kBlockM;
+        const int n0 = (t % sh.tiles_n) * kBlockN;
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -115,8 +129,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_cons
           ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
           const bool seg1 = kb >= sh.kb0;
           const int kk = (seg1 ? kb - sh.kb0 : kb) * kBlockK;
-          const CUtensorMap* ta = seg1 ? &tm_a1 : &tm_a0;
-          const CUtensorMap* tb = seg1 ? &tm_b1 : &tm_b0;
+          const int mi = seg1 ? 1 : group;
+          const CUtensorMap* ta = &maps.a[mi];
+          const CUtensorMap* tb = &maps.b[mi];
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kTileABytes;
           if (!sh.a_mn) {
@@ -185,33 +200,44 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_cons
     __syncwarp();
   } else {
     // ------------------------------ epilogue ------------------------------
-    const int quad = warp & 3;   // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    const int half = (warp - 2) >> 2;       // which 128-column half of the tile
+    constexpr int kChunks = kBlockN / 2 / 32;
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       const uint32_t acc = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
-      const int m0 = (tile / sh.tiles_n) * kBlockM;
-      const int n0 = (tile % sh.tiles_n) * kBlockN;
+      const int group = tile / tiles_per_group;
+      const int t = tile - group * tiles_per_group;
+      const int m0 = (t / sh.tiles_n) * kBlockM;
+      const int col_first = (t % sh.tiles_n) * kBlockN + half * (kBlockN / 2);
+      const int row = m0 + quad * 32 + lane;
+      const int nchunks = min(kChunks, (sh.n - col_first + 31) / 32);   // <= 0: nothing to do
+      const bool active = row < sh.m && nchunks > 0;
+      typename Epi::Ctx ctx;
+      if (active) epi.begin(ctx, group, row, col_first, nchunks);       // overlaps the wait below
       if (!ptx::mbar_wait(&tfull_bar[acc], aph, abort_flag)) {
         *abort_flag = 1;
         atomicCAS(sh.status, 0, (kDevTimeoutEpilogue << 24) | (tcount & 0xFFFFFF));
         break;
       }
       ptx::tc_fence_after_sync();
-      const int row = m0 + quad * 32 + lane;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBlockN;
-#pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= sh.n) break;
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(t_row + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (row < sh.m) {
-          float v[32];
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBlockN +
+                             half * (kBlockN / 2);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          epi(row, col0, v);
+      for (int c = 0; c < kChunks; ++c) {
+        if (c < nchunks) {   // warp-uniform
+          const int col0 = col_first + c * 32;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(t_row + c * 32, r);
+          if (active) epi.prefetch(ctx, row, col0, c);
+          ptx::tmem_ld_wait();
+          if (active) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            epi(ctx, group, row, col0, c, v);
+          }
         }
       }
       ptx::tc_fence_before_sync();

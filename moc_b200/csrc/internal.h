@@ -14,17 +14,20 @@ struct MatOperand {
   int mn_major;   // 0: memory is [mn][k] (K contiguous); 1: memory is [k][mn] (M/N contiguous)
 };
 
-enum EpiKind : int { kEpiStore = 0, kEpiUpSparse = 1, kEpiBwdSparse = 2, kEpiDenseSwiGLU = 3 };
+enum EpiKind : int { kEpiStore = 0, kEpiUpSparse = 1, kEpiDenseSwiGLU = 2 };
+
+constexpr int kGemmMaxGroups = 3;
 
 struct EpiArgs {
   int kind;
-  // kEpiStore
-  void* c;
-  int64_t ldc;
-  int transposed;
-  // sparse epilogues / dense SwiGLU
-  void* dense0;             // up: G -> Z' in place; bwd: dG'; dense: G -> Z
-  void* dense1;             // bwd: dU'; dense: U out (or null)
+  // kEpiStore: one output per group
+  void* c[kGemmMaxGroups];
+  int64_t ldc[kGemmMaxGroups];
+  int transposed[kGemmMaxGroups];
+  // kEpiUpSparse: dense0 = G -> Z' in place. kEpiDenseSwiGLU: dense0 = G (in), dense1 = U (out), dense2 = Z (out)
+  void* dense0;
+  void* dense1;
+  void* dense2;
   int64_t ld_dense;
   const uint32_t* bitmap;
   const uint16_t* rank0;
@@ -33,17 +36,18 @@ struct EpiArgs {
   void* u_sel;
   void* s_sel;
   void* z_sel;
-  const void* g_sel;
 };
 
+// C_g[m, n] = A_g[m, k0] * B_g[n, k0]^T for g < groups, or, with groups == 1 and k1 > 0,
+// C = A_0[m, k0] * B_0[n, k0]^T + A_1[m, k1] * B_1[n, k1]^T.
 struct GemmProblem {
   int dtype;                 // DType
   int impl;                  // 0: default for the dtype (bf16 -> tcgen05, f32 -> SIMT); 1: force SIMT
   int m, n;
-  int k0;                    // K extent of segment 0
-  MatOperand a0, b0;
-  int k1;                    // K extent of segment 1 (0: none)
-  MatOperand a1, b1;
+  int groups;                // 1..3 same-shape problems in one launch
+  int k0;
+  int k1;                    // K extent of the second segment (0: none)
+  MatOperand a[kGemmMaxGroups], b[kGemmMaxGroups];
   EpiArgs epi;
   int* status;               // device status word (may be null for SIMT)
 };
@@ -51,13 +55,17 @@ struct GemmProblem {
 int launch_gemm(const GemmProblem& p, cudaStream_t stream);
 
 // ---- selection / auxiliary kernels (kernels.cu) ---------------------------------------------
-int launch_topk_select(int dtype, const void* g, int64_t ldg, int tokens, int d_ffn, int k, int16_t* idx,
+// write_s != 0: the gate rows (ldg >= ffn_ld) are overwritten in place by S' = mask * round(SiLU(g))
+int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, int write_s, int16_t* idx,
                        void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
-int launch_select_2of8(int dtype, const void* g, int64_t ldg, int tokens, int d_ffn, int16_t* idx, void* g_sel,
+int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int write_s, int16_t* idx, void* g_sel,
                        uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
 // Z'[tokens, ld] <- zero-filled scatter of the compact z (or of round(round(SiLU(g)) * u) when z_sel is null)
-int launch_expand_z(int dtype, const uint32_t* bitmap, const uint16_t* rank0, const void* z_sel, const void* g_sel,
-                    const void* u_sel, void* dense, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
+int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void* g_sel, const void* u_sel, void* dense,
+                    int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
+// dZ[tokens, ld] (in) -> dG' (grad_g_out) and dU' (written over dZ in place): gather, SiLU', zero fill
+int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
+                      void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
 // out[cols, rows] <- in[rows, cols]^T
 int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_t ld_out, int rows, int cols,
                      cudaStream_t stream);
@@ -69,7 +77,7 @@ int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_
 enum ProfTag : int {
   kProfEnd = 0, kProfGemmTc = 1, kProfGemmSimt = 2, kProfTopk = 3, kProfSel2of8 = 4, kProfExpand = 5,
   kProfTranspose = 6, kProfDecodeGate = 7, kProfDecodeUp = 8, kProfDecodeDown = 9, kProfDecodeFused28 = 10,
-  kProfDecodeDense = 11,
+  kProfDecodeDense = 11, kProfBwdSparse = 12,
 };
 void prof_mark(int tag, cudaStream_t stream);
 

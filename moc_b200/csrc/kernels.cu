@@ -3,11 +3,15 @@
 //   topk_select_kernel : row-wise Top-K over d_ffn pre-SiLU gate values. Replaces
 //                        torch.topk (moc/ffn.py:144, :392) and the CUB block sort of the decode
 //                        extension (moc/inference/cuda/optimized_global_moc_ext.cu:85-125) by a
-//                        radix *select*: the K-th largest order key is found bit by bit, ties
-//                        at the threshold go to the lower channel index, and the selected set
-//                        is emitted in ascending channel order together with a bitmap.
+//                        radix *select*: one warp per token finds the K-th largest order key
+//                        digit by digit (11-bit shared-memory histograms), ties at the threshold
+//                        go to the lower channel index, and the selected set is emitted in
+//                        ascending channel order together with a bitmap. On request the gate row
+//                        is overwritten by S' = mask * SiLU(G) for the up-projection epilogue.
 //   select_2of8_kernel : structured top-2 of every 8 consecutive channels (moc/ffn.py:68-108).
 //   expand_z_kernel    : compact z -> zero-filled dense Z' (moc/ffn.py:196-199, :435-442).
+//   bwd_sparse_kernel  : dense dZ -> zero-filled dense dG', dU' through the selected channels
+//                        (moc/ffn.py:219-237, moc/training/triton_sparse_aux.py:363-423).
 //   transpose_kernel   : W_down [d, F] <-> W_down^T [F, d] (moc/inference/inference_ffn.py:104-110).
 #include <cuda_bf16.h>
 #include <stdarg.h>
@@ -25,190 +29,346 @@ template <typename T> struct KeyTraits;
 template <> struct KeyTraits<__nv_bfloat16> {
   using Bits = uint16_t;
   static constexpr int kBits = 16;
-  __device__ __forceinline__ static uint32_t key(Bits b) { return order_key16(b); }
-  __device__ __forceinline__ static Bits unkey(uint32_t k) {
-    return static_cast<Bits>((k & 0x8000u) ? (k ^ 0x8000u) : (k ^ 0xFFFFu));
+  __device__ __forceinline__ static uint32_t key(uint32_t b) { return order_key16(static_cast<uint16_t>(b)); }
+  __device__ __forceinline__ static float value(Bits b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+  __device__ __forceinline__ static Bits bits(float v) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    return *reinterpret_cast<const Bits*>(&h);
   }
 };
 template <> struct KeyTraits<float> {
   using Bits = uint32_t;
   static constexpr int kBits = 32;
-  __device__ __forceinline__ static uint32_t key(Bits b) { return order_key32(b); }
-  __device__ __forceinline__ static Bits unkey(uint32_t k) { return (k & 0x80000000u) ? (k ^ 0x80000000u) : ~k; }
+  __device__ __forceinline__ static uint32_t key(uint32_t b) { return order_key32(b); }
+  __device__ __forceinline__ static float value(Bits b) { return __uint_as_float(b); }
+  __device__ __forceinline__ static Bits bits(float v) { return __float_as_uint(v); }
 };
 
-constexpr int kSelThreads = 256;
-constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kSelWarpsPerCta = 8;
+constexpr int kSelHistWords = 1024;   // 2048 bins of 16 bits, two per word
 
-__device__ __forceinline__ uint32_t block_sum(uint32_t v, uint32_t* red /*[2][kSelWarps]*/, int iter) {
-  const uint32_t w = __reduce_add_sync(0xFFFFFFFFu, v);
-  uint32_t* buf = red + (iter & 1) * kSelWarps;
-  if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = w;
-  __syncthreads();
-  uint32_t tot = 0;
-#pragma unroll
-  for (int i = 0; i < kSelWarps; ++i) tot += buf[i];
-  return tot;
+__device__ __forceinline__ uint32_t hist_count(const uint32_t* hist, int b) {
+  return (hist[b >> 1] >> ((b & 1) * 16)) & 0xFFFFu;
 }
 
-__device__ __forceinline__ uint32_t block_exscan(uint32_t v, uint32_t* wsum /*[kSelWarps]*/, uint32_t& total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// One warp per token row; lane l handles the channels l, l + 32, l + 64, ... so that a warp
+// ballot over one step is exactly one 32-channel word of the selection bitmap and channel
+// order equals (step, lane) order. write_s != 0: the row of g is overwritten in place by
+// S' = selected ? round(SiLU(g)) : 0 over the full padded width 32 * words.
+template <typename T>
+__global__ void __launch_bounds__(kSelWarpsPerCta * 32)
+topk_select_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k, int words, int write_s,
+                   int16_t* __restrict__ idx, T* __restrict__ g_sel, uint32_t* __restrict__ bitmap,
+                   uint16_t* __restrict__ rank0) {
+  using KT = KeyTraits<T>;
+  using Bits = typename KT::Bits;
+  __shared__ uint32_t hist_all[kSelWarpsPerCta][kSelHistWords];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kSelWarpsPerCta + warp;
+  if (row >= tokens) return;   // whole warps leave; no block-wide barrier is used below
+  uint32_t* hist = hist_all[warp];
+  Bits* grow = reinterpret_cast<Bits*>(g) + static_cast<int64_t>(row) * ldg;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+
+  // ---- K-th largest key, one digit per pass, most significant first ----
+  uint32_t prefix = 0, prefix_mask = 0, k_rem = static_cast<uint32_t>(k);
+  int hi_bit = KT::kBits;
+#pragma unroll 1
+  while (hi_bit > 0) {
+    const int nbits = (hi_bit == 32) ? 11 : (hi_bit >= 11 ? 11 : hi_bit);   // 16: 11+5, 32: 11+11+10
+    const int shift = hi_bit - nbits;
+    const int nbins = 1 << nbits;
+    for (int i = lane; i < (nbins >> 1); i += 32) hist[i] = 0u;
+    __syncwarp();
+#pragma unroll 4
+    for (int c = lane; c < d_ffn; c += 32) {
+      const uint32_t key = KT::key(grow[c]);
+      if ((key & prefix_mask) == prefix) {
+        const uint32_t b = (key >> shift) & (nbins - 1);
+        atomicAdd(&hist[b >> 1], 1u << ((b & 1u) * 16));
+      }
+    }
+    __syncwarp();
+    // lane l owns the bins [lo, lo + per) counted from the top; `above` = keys in higher bins
+    const int per = nbins >> 5;   // nbins >= 32
+    const int lo = (31 - lane) * per;
+    uint32_t local = 0;
+    for (int b = 0; b < per; ++b) local += hist_count(hist, lo + b);
+    uint32_t inc = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t nb = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += nb;
+    }
+    uint32_t above = inc - local;
+    const bool mine = above < k_rem && above + local >= k_rem;
+    uint32_t digit = 0, new_k = 0;
+    if (mine) {
+      for (int b = lo + per - 1; b >= lo; --b) {
+        const uint32_t c = hist_count(hist, b);
+        if (above + c >= k_rem) {
+          digit = static_cast<uint32_t>(b);
+          new_k = k_rem - above;
+          break;
+        }
+        above += c;
+      }
+    }
+    const int src = __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1;   // exactly one lane
+    digit = __shfl_sync(0xFFFFFFFFu, digit, src);
+    k_rem = __shfl_sync(0xFFFFFFFFu, new_k, src);
+    prefix |= digit << shift;
+    prefix_mask |= static_cast<uint32_t>(nbins - 1) << shift;
+    hi_bit = shift;
+    __syncwarp();
+  }
+  const uint32_t thr = prefix;        // K-th largest key
+  const uint32_t take_eq = k_rem;     // ties admitted, lowest channels first
+
+  // ---- emit: one bitmap word per step ----
+  int16_t* idx_row = idx + static_cast<int64_t>(row) * k;
+  Bits* gsel_row = reinterpret_cast<Bits*>(g_sel) + static_cast<int64_t>(row) * k;
+  uint32_t* bm_row = bitmap + static_cast<int64_t>(row) * words;
+  uint16_t* rk_row = rank0 + static_cast<int64_t>(row) * words;
+  uint32_t run = 0, eq_seen = 0;
+#pragma unroll 2
+  for (int w = 0; w < words; ++w) {
+    const int c = w * 32 + lane;
+    const bool valid = c < d_ffn;
+    const Bits raw = valid ? grow[c] : Bits(0);
+    const uint32_t key = KT::key(raw);
+    const bool is_eq = valid && key == thr;
+    const uint32_t eq_ballot = __ballot_sync(0xFFFFFFFFu, is_eq);
+    const bool sel = valid && (key > thr || (is_eq && eq_seen + __popc(eq_ballot & lt_mask) < take_eq));
+    const uint32_t word = __ballot_sync(0xFFFFFFFFu, sel);
+    if (sel) {
+      const uint32_t pos = run + __popc(word & lt_mask);
+      idx_row[pos] = static_cast<int16_t>(c);
+      gsel_row[pos] = raw;
+    }
+    if (write_s) grow[c] = sel ? KT::bits(silu_round<T>(KT::value(raw))) : Bits(0);
+    if (lane == 0) {
+      bm_row[w] = word;
+      rk_row[w] = static_cast<uint16_t>(run);
+    }
+    run += __popc(word);
+    eq_seen += __popc(eq_ballot);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// bf16 fast path of the Top-K selection: one warp per token, 16-byte loads of 8 channels per
+// lane (vector v = slot * 32 + lane), packed 16-bit order keys. Needs 16-byte aligned rows padded
+// to 32 * words elements.
+// ------------------------------------------------------------------------------------------
+constexpr int kVecSelWarps = 4;
+constexpr int kVecSelBins = 2048;
+
+__device__ __forceinline__ uint32_t keys2_from_bits(uint32_t x) {   // two bf16 patterns -> two order keys
+  const uint32_t m = (x >> 15) & 0x00010001u;
+  return x ^ 0x80008000u ^ (m * 0x7FFFu);
+}
+__device__ __forceinline__ uint32_t bits_from_key16(uint32_t key) {
+  return (key & 0x8000u) ? (key ^ 0x8000u) : (key ^ 0xFFFFu);
+}
+__device__ __forceinline__ uint32_t warp_exscan(uint32_t v, uint32_t& total) {
+  const int lane = threadIdx.x & 31;
   uint32_t inc = v;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const uint32_t nb = __shfl_up_sync(0xFFFFFFFFu, inc, o);
     if (lane >= o) inc += nb;
   }
-  if (lane == 31) wsum[warp] = inc;
-  __syncthreads();
-  uint32_t woff = 0, tot = 0;
-#pragma unroll
-  for (int i = 0; i < kSelWarps; ++i) {
-    const uint32_t s = wsum[i];
-    if (i < warp) woff += s;
-    tot += s;
-  }
-  total = tot;
-  __syncthreads();
-  return woff + inc - v;
+  total = __shfl_sync(0xFFFFFFFFu, inc, 31);
+  return inc - v;
 }
 
-// One CTA per token row. Thread t owns the contiguous channels [t*chunk, (t+1)*chunk), so
-// walking the threads in order walks the channels in order. REG > 0: the thread keeps its
-// keys in REG registers (chunk <= REG); REG == 0: keys stay in shared memory.
-template <typename T, int REG>
-__global__ void __launch_bounds__(kSelThreads)
-topk_select_kernel(const T* __restrict__ g, int64_t ldg, int d_ffn, int k, int words, int16_t* __restrict__ idx,
-                   T* __restrict__ g_sel, uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
-  using KT = KeyTraits<T>;
-  using Bits = typename KT::Bits;
-  extern __shared__ __align__(16) uint8_t sel_smem[];
-  uint32_t* bm = reinterpret_cast<uint32_t*>(sel_smem);                    // [words]
-  Bits* keys = reinterpret_cast<Bits*>(sel_smem + sizeof(uint32_t) * words);   // [d_ffn] order keys
-  __shared__ uint32_t red[2 * kSelWarps];
-  __shared__ uint32_t wsum[kSelWarps];
-
-  const int row = blockIdx.x;
-  const int tid = threadIdx.x;
-  const Bits* grow = reinterpret_cast<const Bits*>(g) + static_cast<int64_t>(row) * ldg;
-
-  for (int i = tid; i < d_ffn; i += kSelThreads) keys[i] = static_cast<Bits>(KT::key(grow[i]));
-  for (int w = tid; w < words; w += kSelThreads) bm[w] = 0u;
-  __syncthreads();
-
-  const int chunk = (d_ffn + kSelThreads - 1) / kSelThreads;
-  const int begin = min(tid * chunk, d_ffn);
-  const int end = min(begin + chunk, d_ffn);
-  const int mine = end - begin;
-
-  uint32_t kr[REG > 0 ? REG : 1];
-  if (REG > 0) {
+// Order keys of vector v of a padded row (8 channels, two per word); channels >= d_ffn get key 0,
+// which is below every real key.
+__device__ __forceinline__ void load_keys8(const uint4* grow4, int v, int nvec, int d_ffn, uint32_t (&a)[4]) {
+  uint4 q = make_uint4(0u, 0u, 0u, 0u);
+  if (v < nvec) q = grow4[v];
+  a[0] = keys2_from_bits(q.x);
+  a[1] = keys2_from_bits(q.y);
+  a[2] = keys2_from_bits(q.z);
+  a[3] = keys2_from_bits(q.w);
+  const int nval = d_ffn - 8 * v;
+  if (nval < 8) {
 #pragma unroll
-    for (int i = 0; i < REG; ++i) kr[i] = (i < mine) ? static_cast<uint32_t>(keys[begin + i]) : 0u;
-  }
-
-  // K-th largest key, most significant bit first: the largest t with count(key >= t) >= k.
-  uint32_t thr = 0;
-#pragma unroll 1
-  for (int bit = KT::kBits - 1; bit >= 0; --bit) {
-    const uint32_t cand = thr | (1u << bit);
-    uint32_t cnt = 0;
-    if (REG > 0) {
-#pragma unroll
-      for (int i = 0; i < REG; ++i) cnt += (kr[i] >= cand) ? 1u : 0u;   // padding keys are 0 < cand
-    } else {
-      for (int i = begin; i < end; ++i) cnt += (static_cast<uint32_t>(keys[i]) >= cand) ? 1u : 0u;
+    for (int j = 0; j < 4; ++j) {
+      if (2 * j >= nval) a[j] = 0u;
+      else if (2 * j + 1 >= nval) a[j] &= 0xFFFFu;
     }
-    if (block_sum(cnt, red, bit) >= static_cast<uint32_t>(k)) thr = cand;
   }
+}
 
-  // counts above / equal to the threshold in front of this thread's chunk
-  uint32_t n_gt = 0, n_eq = 0;
-  if (REG > 0) {
+// The row is re-read for each of the three passes (two histogram passes, one emit pass); with
+// a few warps per SM it stays in L1, so HBM sees it once. Loops are kept rolled: the kernel is
+// issue-bound and a fully unrolled body thrashes the instruction cache.
+__global__ void __launch_bounds__(kVecSelWarps * 32)
+topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k, int words,
+                            int write_s, int16_t* __restrict__ idx, uint16_t* __restrict__ g_sel,
+                            uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
+  __shared__ uint32_t hist_all[kVecSelWarps][kVecSelBins];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kVecSelWarps + warp;
+  if (row >= tokens) return;   // whole warps leave; only warp-level synchronisation below
+  uint32_t* hist = hist_all[warp];
+  uint16_t* grow = g + static_cast<int64_t>(row) * ldg;
+  uint4* grow4 = reinterpret_cast<uint4*>(grow);
+  const int nvec = words * 4;                       // 16-byte vectors in the padded row
+  const int nslots = (nvec + 31) >> 5;              // vector v = slot * 32 + lane
+
+  // ---- digit 1: the upper 11 key bits ----
+  {
+    uint4* h4 = reinterpret_cast<uint4*>(hist);
+    for (int i = lane; i < kVecSelBins / 4; i += 32) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  __syncwarp();
+#pragma unroll 2
+  for (int i = 0; i < nslots; ++i) {
+    const int v = i * 32 + lane;
+    uint32_t a[4];
+    load_keys8(grow4, v, nvec, d_ffn, a);
+    if (v * 8 < d_ffn) {
 #pragma unroll
-    for (int i = 0; i < REG; ++i) {
-      if (i < mine) {
-        n_gt += (kr[i] > thr) ? 1u : 0u;
-        n_eq += (kr[i] == thr) ? 1u : 0u;
+      for (int j = 0; j < 4; ++j) {
+        atomicAdd(&hist[(a[j] & 0xFFFFu) >> 5], 1u);
+        atomicAdd(&hist[a[j] >> 21], 1u);
       }
     }
-  } else {
-    for (int i = begin; i < end; ++i) {
-      const uint32_t key = keys[i];
-      n_gt += (key > thr) ? 1u : 0u;
-      n_eq += (key == thr) ? 1u : 0u;
+  }
+  __syncwarp();
+  uint32_t k_rem = static_cast<uint32_t>(k);
+  uint32_t digit1, digit2;
+  {
+    // lane l sums the 64 bins [lo, lo + 64) counted from the top (rotated start: no bank conflicts)
+    const int lo = (31 - lane) * 64;
+    uint32_t local = 0;
+#pragma unroll 8
+    for (int j = 0; j < 64; ++j) local += hist[lo + ((j + lane) & 63)];
+    uint32_t total;
+    const uint32_t above = warp_exscan(local, total);
+    const bool mine = above < k_rem && above + local >= k_rem;
+    const int src = __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1;
+    const uint32_t above_src = __shfl_sync(0xFFFFFFFFu, above, src);
+    const int top = (31 - src) * 64 + 63;            // highest bin of the owning range
+    const uint32_t c0 = hist[top - 2 * lane], c1 = hist[top - 2 * lane - 1];
+    const uint32_t ex = warp_exscan(c0 + c1, total) + above_src;
+    const bool hit = ex < k_rem && ex + c0 + c1 >= k_rem;
+    uint32_t d = 0, nk = 0;
+    if (hit) {
+      if (ex + c0 >= k_rem) { d = top - 2 * lane; nk = k_rem - ex; }
+      else { d = top - 2 * lane - 1; nk = k_rem - ex - c0; }
+    }
+    const int src2 = __ffs(__ballot_sync(0xFFFFFFFFu, hit)) - 1;
+    digit1 = __shfl_sync(0xFFFFFFFFu, d, src2);
+    k_rem = __shfl_sync(0xFFFFFFFFu, nk, src2);
+  }
+  __syncwarp();
+
+  // ---- digit 2: the lower 5 key bits of the keys that share digit 1 ----
+  hist[lane] = 0u;
+  __syncwarp();
+#pragma unroll 2
+  for (int i = 0; i < nslots; ++i) {
+    uint32_t a[4];
+    load_keys8(grow4, i * 32 + lane, nvec, d_ffn, a);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo16 = a[j] & 0xFFFFu, hi16 = a[j] >> 16;
+      if ((lo16 >> 5) == digit1) atomicAdd(&hist[lo16 & 31u], 1u);
+      if ((hi16 >> 5) == digit1) atomicAdd(&hist[hi16 & 31u], 1u);
     }
   }
-  uint32_t total = 0;
-  const uint32_t ex = block_exscan(n_gt | (n_eq << 16), wsum, total);
-  const uint32_t gt_before = ex & 0xFFFFu, eq_before = ex >> 16;
-  const uint32_t take_eq = static_cast<uint32_t>(k) - (total & 0xFFFFu);   // ties admitted, lowest channels first
-  uint32_t eq_seen = eq_before;
-  uint32_t pos = gt_before + min(eq_before, take_eq);
+  __syncwarp();
+  {
+    const uint32_t c = hist[31 - lane];
+    uint32_t total;
+    const uint32_t ex = warp_exscan(c, total);
+    const bool hit = ex < k_rem && ex + c >= k_rem;
+    const int src = __ffs(__ballot_sync(0xFFFFFFFFu, hit)) - 1;
+    digit2 = 31 - src;
+    k_rem = k_rem - __shfl_sync(0xFFFFFFFFu, ex, src);
+  }
+  const uint32_t thr = (digit1 << 5) | digit2;   // K-th largest key
+  const uint32_t take_eq = k_rem;                // ties admitted, lowest channels first
 
+  // ---- emit ----
   int16_t* idx_row = idx + static_cast<int64_t>(row) * k;
-  Bits* gsel_row = reinterpret_cast<Bits*>(g_sel) + static_cast<int64_t>(row) * k;
-  int cur_w = -1;
-  uint32_t cur_m = 0;
-  auto visit = [&](int ch, uint32_t key) {
-    bool sel = key > thr;
-    if (key == thr) {
-      sel = eq_seen < take_eq;
-      ++eq_seen;
-    }
-    if (sel) {
-      idx_row[pos] = static_cast<int16_t>(ch);
-      gsel_row[pos] = KT::unkey(key);
-      ++pos;
-      const int w = ch >> 5;
-      if (w != cur_w) {
-        if (cur_m) atomicOr(&bm[cur_w], cur_m);
-        cur_w = w;
-        cur_m = 0;
-      }
-      cur_m |= 1u << (ch & 31);
-    }
-  };
-  if (REG > 0) {
-#pragma unroll
-    for (int i = 0; i < REG; ++i)
-      if (i < mine) visit(begin + i, kr[i]);
-  } else {
-    for (int i = begin; i < end; ++i) visit(i, keys[i]);
-  }
-  if (cur_m) atomicOr(&bm[cur_w], cur_m);
-  __syncthreads();
-
-  // bitmap words and the rank of each word's first channel
-  const int wchunk = (words + kSelThreads - 1) / kSelThreads;
-  const int wb = min(tid * wchunk, words), we = min(wb + wchunk, words);
-  uint32_t pc = 0;
-  for (int w = wb; w < we; ++w) pc += __popc(bm[w]);
-  uint32_t tot2 = 0;
-  uint32_t run = block_exscan(pc, wsum, tot2);
+  uint16_t* gsel_row = g_sel + static_cast<int64_t>(row) * k;
   uint32_t* bm_row = bitmap + static_cast<int64_t>(row) * words;
   uint16_t* rk_row = rank0 + static_cast<int64_t>(row) * words;
-  for (int w = wb; w < we; ++w) {
-    const uint32_t m = bm[w];
-    bm_row[w] = m;
-    rk_row[w] = static_cast<uint16_t>(run);
-    run += __popc(m);
+  uint32_t run = 0, eq_seen = 0;
+#pragma unroll 1
+  for (int i = 0; i < nslots; ++i) {
+    const int v = i * 32 + lane;
+    uint32_t a[4];
+    load_keys8(grow4, v, nvec, d_ffn, a);
+    uint32_t gtm = 0, eqm = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo16 = a[j] & 0xFFFFu, hi16 = a[j] >> 16;
+      gtm |= (lo16 > thr ? 1u : 0u) << (2 * j);
+      gtm |= (hi16 > thr ? 1u : 0u) << (2 * j + 1);
+      eqm |= (lo16 == thr ? 1u : 0u) << (2 * j);
+      eqm |= (hi16 == thr ? 1u : 0u) << (2 * j + 1);
+    }
+    uint32_t tot_eq, tot_sel;
+    const uint32_t ex_eq = warp_exscan(__popc(eqm), tot_eq);
+    const int allowed = static_cast<int>(take_eq) - static_cast<int>(eq_seen + ex_eq);
+    uint32_t sel_eq = allowed > 0 ? eqm : 0u;
+    while (static_cast<int>(__popc(sel_eq)) > allowed && sel_eq) sel_eq &= ~(0x80000000u >> __clz(sel_eq));
+    const uint32_t selm = gtm | sel_eq;
+    const uint32_t ex_sel = warp_exscan(__popc(selm), tot_sel);
+    uint32_t b = selm << (8 * (lane & 3));
+    b |= __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+    b |= __shfl_xor_sync(0xFFFFFFFFu, b, 2);
+    const int widx = i * 8 + (lane >> 2);
+    if ((lane & 3) == 0 && widx < words) {
+      bm_row[widx] = b;
+      rk_row[widx] = static_cast<uint16_t>(run + ex_sel);
+    }
+    uint32_t pos = run + ex_sel;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if ((selm >> j) & 1u) {
+        const uint32_t key16 = (a[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+        idx_row[pos] = static_cast<int16_t>(8 * v + j);
+        gsel_row[pos] = static_cast<uint16_t>(bits_from_key16(key16));
+        ++pos;
+      }
+    }
+    if (write_s && v < nvec) grow4[v] = make_uint4(0u, 0u, 0u, 0u);   // selected channels: filled in below
+    run += tot_sel;
+    eq_seen += tot_eq;
+  }
+
+  // ---- S' = round(SiLU(g)) of the selected channels, computed in compact space (full lanes) ----
+  if (write_s) {
+    __syncwarp();   // orders the zero fill and the compact outputs above before the accesses below
+    for (int p = lane; p < k; p += 32) {
+      const int ch = idx_row[p];
+      const float gv = __uint_as_float(static_cast<uint32_t>(gsel_row[p]) << 16);
+      const __nv_bfloat16 s = __float2bfloat16_rn(gv * sigmoid_act<__nv_bfloat16>(gv));
+      grow[ch] = *reinterpret_cast<const uint16_t*>(&s);
+    }
   }
 }
 
 // One thread per (token, 32-channel word) = 4 groups of 8. Lower channel index wins ties
-// (moc/inference/triton_fused_ffn_kernels.py:103-114).
+// (moc/inference/triton_fused_ffn_kernels.py:103-114). write_s: as in topk_select_kernel.
 template <typename T>
-__global__ void select_2of8_kernel(const T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k_eff, int words,
-                                   int16_t* __restrict__ idx, T* __restrict__ g_sel, uint32_t* __restrict__ bitmap,
-                                   uint16_t* __restrict__ rank0) {
+__global__ void select_2of8_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k_eff, int words,
+                                   int write_s, int16_t* __restrict__ idx, T* __restrict__ g_sel,
+                                   uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
   using KT = KeyTraits<T>;
   using Bits = typename KT::Bits;
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (gid >= static_cast<int64_t>(tokens) * words) return;
   const int row = static_cast<int>(gid / words);
   const int w = static_cast<int>(gid % words);
-  const Bits* grow = reinterpret_cast<const Bits*>(g) + static_cast<int64_t>(row) * ldg;
+  Bits* grow = reinterpret_cast<Bits*>(g) + static_cast<int64_t>(row) * ldg;
   int16_t* idx_row = idx + static_cast<int64_t>(row) * k_eff;
   Bits* gsel_row = reinterpret_cast<Bits*>(g_sel) + static_cast<int64_t>(row) * k_eff;
   uint32_t mask = 0;
@@ -216,68 +376,125 @@ __global__ void select_2of8_kernel(const T* __restrict__ g, int64_t ldg, int tok
   for (int q = 0; q < 4; ++q) {
     const int c0 = w * 32 + q * 8;
     const int nv = min(8, d_ffn - c0);
-    if (nv <= 0) break;
+    Bits raw[8];
     uint32_t key[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) key[j] = (j < nv) ? KT::key(grow[c0 + j]) : 0u;
-    int b1 = 0;
+    for (int j = 0; j < 8; ++j) {
+      raw[j] = (j < nv) ? grow[c0 + j] : Bits(0);
+      key[j] = KT::key(raw[j]);
+    }
+    int lo = -1, hi = -1;
+    if (nv > 0) {
+      int b1 = 0;
 #pragma unroll
-    for (int j = 1; j < 8; ++j)
-      if (j < nv && key[j] > key[b1]) b1 = j;
-    int b2 = -1;
-    if (nv >= 2) {
+      for (int j = 1; j < 8; ++j)
+        if (j < nv && key[j] > key[b1]) b1 = j;
+      int b2 = -1;
+      if (nv >= 2) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j < nv && j != b1 && (b2 < 0 || key[j] > key[b2])) b2 = j;
+      }
+      lo = (b2 >= 0 && b2 < b1) ? b2 : b1;
+      hi = (b2 >= 0 && b2 < b1) ? b1 : b2;
+      const int pos = (c0 >> 3) * 2;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {   // constant-index register reads only
+        if (j == lo) {
+          idx_row[pos] = static_cast<int16_t>(c0 + j);
+          gsel_row[pos] = raw[j];
+        }
+        if (j == hi) {
+          idx_row[pos + 1] = static_cast<int16_t>(c0 + j);
+          gsel_row[pos + 1] = raw[j];
+        }
+      }
+      mask |= 1u << (q * 8 + lo);
+      if (hi >= 0) mask |= 1u << (q * 8 + hi);
+    }
+    if (write_s) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (j < nv && j != b1 && (b2 < 0 || key[j] > key[b2])) b2 = j;
-    }
-    const int pos = (c0 >> 3) * 2;
-    const int lo = (b2 >= 0 && b2 < b1) ? b2 : b1;
-    const int hi = (b2 >= 0 && b2 < b1) ? b1 : b2;
-    idx_row[pos] = static_cast<int16_t>(c0 + lo);
-    gsel_row[pos] = KT::unkey(key[lo]);
-    mask |= 1u << (q * 8 + lo);
-    if (hi >= 0) {
-      idx_row[pos + 1] = static_cast<int16_t>(c0 + hi);
-      gsel_row[pos + 1] = KT::unkey(key[hi]);
-      mask |= 1u << (q * 8 + hi);
+        grow[c0 + j] = (j == lo || j == hi) ? KT::bits(silu_round<T>(KT::value(raw[j]))) : Bits(0);
     }
   }
   bitmap[gid] = mask;
   rank0[gid] = static_cast<uint16_t>(min(w * 8, k_eff));
 }
 
-// One thread per (token, word): writes 32 dense values.
+// The two dense <-> compact kernels below run one CTA per token and work in COMPACT space: every
+// thread handles selected channels only (full lanes for the SiLU math), scatters its results
+// into a zeroed shared-memory image of the dense row, and the CTA then writes the row out
+// with 16-byte coalesced stores.
+constexpr int kRowThreads = 256;
+
 template <typename T>
-__global__ void expand_z_kernel(const uint32_t* __restrict__ bitmap, const uint16_t* __restrict__ rank0,
-                                const T* __restrict__ z_sel, const T* __restrict__ g_sel, const T* __restrict__ u_sel,
-                                T* __restrict__ dense, int64_t ld, int tokens, int words, int k) {
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= static_cast<int64_t>(tokens) * words) return;
-  const int row = static_cast<int>(gid / words);
-  const int w = static_cast<int>(gid % words);
-  const uint32_t word = bitmap[gid];
-  const int base = rank0[gid];
+__device__ __forceinline__ void row_zero(T* row, int ld) {
+  uint4* r4 = reinterpret_cast<uint4*>(row);
+  const int nvec = ld * static_cast<int>(sizeof(T)) / 16;
+  for (int v = threadIdx.x; v < nvec; v += kRowThreads) r4[v] = make_uint4(0, 0, 0, 0);
+}
+template <typename T>
+__device__ __forceinline__ void row_store(const T* row, T* dst, int ld) {
+  const uint4* r4 = reinterpret_cast<const uint4*>(row);
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  const int nvec = ld * static_cast<int>(sizeof(T)) / 16;
+  for (int v = threadIdx.x; v < nvec; v += kRowThreads) d4[v] = r4[v];
+}
+
+// Z'[token, :] = scatter of z_sel (or of round(round(SiLU(g)) * u) when z_sel is null).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+expand_z_kernel(const int16_t* __restrict__ idx, const T* __restrict__ z_sel, const T* __restrict__ g_sel,
+                const T* __restrict__ u_sel, T* __restrict__ dense, int64_t ld, int k) {
+  extern __shared__ __align__(16) uint8_t row_smem[];
+  T* zrow = reinterpret_cast<T*>(row_smem);
+  const int row = blockIdx.x;
   const int64_t crow = static_cast<int64_t>(row) * k;
-  T* out = dense + static_cast<int64_t>(row) * ld + w * 32;
-  __align__(16) T vals[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float z = 0.0f;
-    if ((word >> j) & 1u) {
-      const int pos = base + __popc(word & ((1u << j) - 1u));
-      if (z_sel) {
-        z = Num<T>::to_float(z_sel[crow + pos]);
-      } else {
-        float s;
-        moc_fwd_point<T>(Num<T>::to_float(g_sel[crow + pos]), Num<T>::to_float(u_sel[crow + pos]), s, z);
-      }
+  row_zero(zrow, static_cast<int>(ld));
+  __syncthreads();
+  for (int p = threadIdx.x; p < k; p += kRowThreads) {
+    const int ch = idx[crow + p];
+    float z;
+    if (z_sel) {
+      z = Num<T>::to_float(z_sel[crow + p]);
+    } else {
+      float s;
+      moc_fwd_point<T>(Num<T>::to_float(g_sel[crow + p]), Num<T>::to_float(u_sel[crow + p]), s, z);
     }
-    vals[j] = Num<T>::from_float(z);
+    zrow[ch] = Num<T>::from_float(z);
   }
-  uint4* o4 = reinterpret_cast<uint4*>(out);
-  const uint4* v4 = reinterpret_cast<const uint4*>(vals);
-#pragma unroll
-  for (int i = 0; i < static_cast<int>(32 * sizeof(T) / 16); ++i) o4[i] = v4[i];
+  __syncthreads();
+  row_store(zrow, dense + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
+}
+
+// dZ (dense, rounded GEMM output) -> dG', dU' (dense, zero outside the selected channels).
+// dU' overwrites dZ in place, dG' goes to its own buffer.
+// gz = dZ, grad_s = round(u * gz), grad_u = round(s * gz), grad_g = round(grad_s * SiLU'(g)), with
+// s = round(SiLU(g)) recomputed from g (identical to the saved s of the reference, moc/ffn.py:157).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+bwd_sparse_kernel(const int16_t* __restrict__ idx, const T* __restrict__ g_sel, const T* __restrict__ u_sel,
+                  T* __restrict__ dz_du, T* __restrict__ grad_g, int64_t ld, int k) {
+  extern __shared__ __align__(16) uint8_t row_smem[];
+  T* grow = reinterpret_cast<T*>(row_smem);
+  T* urow = grow + ld;
+  const int row = blockIdx.x;
+  const int64_t crow = static_cast<int64_t>(row) * k;
+  T* dzrow = dz_du + static_cast<int64_t>(row) * ld;
+  row_zero(grow, static_cast<int>(2 * ld));
+  __syncthreads();
+  for (int p = threadIdx.x; p < k; p += kRowThreads) {
+    const int ch = idx[crow + p];
+    float gg, gu;
+    moc_bwd_point<T>(Num<T>::to_float(g_sel[crow + p]), Num<T>::to_float(u_sel[crow + p]),
+                     Num<T>::to_float(dzrow[ch]), gg, gu);
+    grow[ch] = Num<T>::from_float(gg);
+    urow[ch] = Num<T>::from_float(gu);
+  }
+  __syncthreads();   // all gathers from dZ are done before the row is overwritten
+  row_store(grow, grad_g + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
+  row_store(urow, dzrow, static_cast<int>(ld));
 }
 
 template <typename T>
@@ -299,47 +516,44 @@ __global__ void transpose_kernel(const T* __restrict__ in, int64_t ld_in, T* __r
 // ------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------
-template <typename T>
-static int topk_select_t(const void* g, int64_t ldg, int tokens, int d_ffn, int k, int16_t* idx, void* g_sel,
-                         uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
-  using Bits = typename KeyTraits<T>::Bits;
+int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, int write_s, int16_t* idx,
+                       void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
+  if (tokens == 0) return kOk;
   const int words = static_cast<int>(mask_words(d_ffn));
-  const size_t smem = sizeof(uint32_t) * words + sizeof(Bits) * d_ffn;
-  const int chunk = (d_ffn + kSelThreads - 1) / kSelThreads;
-  const T* gp = static_cast<const T*>(g);
-  T* gs = static_cast<T*>(g_sel);
-#define MOC_SEL_LAUNCH(REG)                                                                                      \
-  do {                                                                                                           \
-    auto kern = topk_select_kernel<T, REG>;                                                                      \
-    if (smem > 48 * 1024) {                                                                                      \
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=     \
-          cudaSuccess)                                                                                           \
-        return check_last("topk_select smem attribute");                                                         \
-    }                                                                                                            \
-    prof_mark(kProfTopk, stream);                                                                                \
-    kern<<<tokens, kSelThreads, smem, stream>>>(gp, ldg, d_ffn, k, words, idx, gs, bitmap, rank0);               \
-  } while (0)
-  if (chunk <= 8) MOC_SEL_LAUNCH(8);
-  else if (chunk <= 16) MOC_SEL_LAUNCH(16);
-  else if (chunk <= 24) MOC_SEL_LAUNCH(24);
-  else if (chunk <= 32) MOC_SEL_LAUNCH(32);
-  else MOC_SEL_LAUNCH(0);
-#undef MOC_SEL_LAUNCH
+  if (write_s && ldg < static_cast<int64_t>(words) * 32) {
+    set_error("select: in-place S' output needs ldg >= %d", words * 32);
+    return kErrInvalidArg;
+  }
+  prof_mark(kProfTopk, stream);
+  // bf16 fast path: needs aligned rows padded to the mask width
+  if (dtype == kBF16 && ldg >= static_cast<int64_t>(words) * 32 && ldg % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(g) & 15u) == 0) {
+    const unsigned vblocks = static_cast<unsigned>((tokens + kVecSelWarps - 1) / kVecSelWarps);
+    uint16_t* gp = static_cast<uint16_t*>(g);
+    uint16_t* gs = static_cast<uint16_t*>(g_sel);
+    topk_select_bf16_vec_kernel<<<vblocks, kVecSelWarps * 32, 0, stream>>>(gp, ldg, tokens, d_ffn, k, words, write_s,
+                                                                         idx, gs, bitmap, rank0);
+    return check_last("topk_select");
+  }
+  const unsigned blocks = static_cast<unsigned>((tokens + kSelWarpsPerCta - 1) / kSelWarpsPerCta);
+  if (dtype == kBF16)
+    topk_select_kernel<__nv_bfloat16><<<blocks, kSelWarpsPerCta * 32, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k, words, write_s, idx, static_cast<__nv_bfloat16*>(g_sel),
+        bitmap, rank0);
+  else
+    topk_select_kernel<float><<<blocks, kSelWarpsPerCta * 32, 0, stream>>>(
+        static_cast<float*>(g), ldg, tokens, d_ffn, k, words, write_s, idx, static_cast<float*>(g_sel), bitmap, rank0);
   return check_last("topk_select");
 }
 
-int launch_topk_select(int dtype, const void* g, int64_t ldg, int tokens, int d_ffn, int k, int16_t* idx,
-                       void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
-  if (tokens == 0) return kOk;
-  if (dtype == kBF16)
-    return topk_select_t<__nv_bfloat16>(g, ldg, tokens, d_ffn, k, idx, g_sel, bitmap, rank0, stream);
-  return topk_select_t<float>(g, ldg, tokens, d_ffn, k, idx, g_sel, bitmap, rank0, stream);
-}
-
-int launch_select_2of8(int dtype, const void* g, int64_t ldg, int tokens, int d_ffn, int16_t* idx, void* g_sel,
+int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int write_s, int16_t* idx, void* g_sel,
                        uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
   if (tokens == 0) return kOk;
   const int words = static_cast<int>(mask_words(d_ffn));
+  if (write_s && ldg < static_cast<int64_t>(words) * 32) {
+    set_error("select: in-place S' output needs ldg >= %d", words * 32);
+    return kErrInvalidArg;
+  }
   const int k_eff = (d_ffn / 8) * 2 + min(2, d_ffn % 8);
   const int64_t total = static_cast<int64_t>(tokens) * words;
   const int threads = 128;
@@ -347,33 +561,74 @@ int launch_select_2of8(int dtype, const void* g, int64_t ldg, int tokens, int d_
   prof_mark(kProfSel2of8, stream);
   if (dtype == kBF16)
     select_2of8_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(g), ldg, tokens, d_ffn, k_eff, words, idx,
+        static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k_eff, words, write_s, idx,
         static_cast<__nv_bfloat16*>(g_sel), bitmap, rank0);
   else
-    select_2of8_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(g), ldg, tokens, d_ffn,
-                                                              k_eff, words, idx, static_cast<float*>(g_sel), bitmap,
-                                                              rank0);
+    select_2of8_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<float*>(g), ldg, tokens, d_ffn, k_eff, words,
+                                                              write_s, idx, static_cast<float*>(g_sel), bitmap, rank0);
   return check_last("select_2of8");
 }
 
-int launch_expand_z(int dtype, const uint32_t* bitmap, const uint16_t* rank0, const void* z_sel, const void* g_sel,
-                    const void* u_sel, void* dense, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream) {
+template <typename T, class Kern>
+static int row_smem_setup(Kern kern, size_t smem, const char* what) {
+  if (smem > 220 * 1024) {
+    set_error("%s: d_ffn too large for the %zu-byte row image in shared memory", what, smem);
+    return kErrUnsupported;
+  }
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return check_last(what);
+  return kOk;
+}
+
+int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void* g_sel, const void* u_sel, void* dense,
+                    int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream) {
+  (void)d_ffn;
   if (tokens == 0) return kOk;
-  const int words = static_cast<int>(mask_words(d_ffn));
-  const int64_t total = static_cast<int64_t>(tokens) * words;
-  const int threads = 128;
-  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-  prof_mark(kProfExpand, stream);
-  if (dtype == kBF16)
-    expand_z_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        bitmap, rank0, static_cast<const __nv_bfloat16*>(z_sel), static_cast<const __nv_bfloat16*>(g_sel),
-        static_cast<const __nv_bfloat16*>(u_sel), static_cast<__nv_bfloat16*>(dense), ld, tokens, words, k);
-  else
-    expand_z_kernel<float><<<blocks, threads, 0, stream>>>(bitmap, rank0, static_cast<const float*>(z_sel),
-                                                           static_cast<const float*>(g_sel),
-                                                           static_cast<const float*>(u_sel),
-                                                           static_cast<float*>(dense), ld, tokens, words, k);
+  int rc;
+  if (dtype == kBF16) {
+    using T = __nv_bfloat16;
+    const size_t smem = ld * sizeof(T);
+    if ((rc = row_smem_setup<T>(expand_z_kernel<T>, smem, "expand_z")) != kOk) return rc;
+    prof_mark(kProfExpand, stream);
+    expand_z_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(z_sel),
+                                                              static_cast<const T*>(g_sel), static_cast<const T*>(u_sel),
+                                                              static_cast<T*>(dense), ld, k);
+  } else {
+    using T = float;
+    const size_t smem = ld * sizeof(T);
+    if ((rc = row_smem_setup<T>(expand_z_kernel<T>, smem, "expand_z")) != kOk) return rc;
+    prof_mark(kProfExpand, stream);
+    expand_z_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(z_sel),
+                                                              static_cast<const T*>(g_sel), static_cast<const T*>(u_sel),
+                                                              static_cast<T*>(dense), ld, k);
+  }
   return check_last("expand_z");
+}
+
+int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
+                      void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream) {
+  (void)d_ffn;
+  if (tokens == 0) return kOk;
+  int rc;
+  if (dtype == kBF16) {
+    using T = __nv_bfloat16;
+    const size_t smem = 2 * ld * sizeof(T);
+    if ((rc = row_smem_setup<T>(bwd_sparse_kernel<T>, smem, "bwd_sparse")) != kOk) return rc;
+    prof_mark(kProfBwdSparse, stream);
+    bwd_sparse_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(g_sel),
+                                                                static_cast<const T*>(u_sel), static_cast<T*>(dz_to_du),
+                                                                static_cast<T*>(grad_g_out), ld, k);
+  } else {
+    using T = float;
+    const size_t smem = 2 * ld * sizeof(T);
+    if ((rc = row_smem_setup<T>(bwd_sparse_kernel<T>, smem, "bwd_sparse")) != kOk) return rc;
+    prof_mark(kProfBwdSparse, stream);
+    bwd_sparse_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(g_sel),
+                                                                static_cast<const T*>(u_sel), static_cast<T*>(dz_to_du),
+                                                                static_cast<T*>(grad_g_out), ld, k);
+  }
+  return check_last("bwd_sparse");
 }
 
 int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_t ld_out, int rows, int cols,

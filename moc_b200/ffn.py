@@ -79,7 +79,7 @@ def moc_ffn_forward(x2d, gate_w, up_w, down_w_t, k: int, select: int, save_sz: b
     return y, idx, g_sel, u_sel, s_sel, z_sel, bitmap, rank0
 
 
-def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, bitmap, rank0, g_sel, u_sel, s_sel, z_sel,
+def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, idx, g_sel, u_sel, s_sel, z_sel,
                      grad_events=None):
     """One MoC FFN backward through ``moc_ffn_bwd``. Returns (dx, d_gate_w, d_up_w, d_down_w) in
     the dtype of the inputs. ``grad_events``: optional (ev_down, ev_gate, ev_up) torch.cuda.Event
@@ -101,7 +101,7 @@ def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, bitmap, rank0, g_sel
     if grad_events is not None:
         evs = [e.cuda_event if e is not None else None for e in grad_events]
     rc = lib.moc_ffn_bwd(code, tokens, d, d_ffn, k, grad_y2d.data_ptr(), x2d.data_ptr(), gate_w.data_ptr(),
-                         up_w.data_ptr(), down_w_t.data_ptr(), bitmap.data_ptr(), rank0.data_ptr(), g_sel.data_ptr(),
+                         up_w.data_ptr(), down_w_t.data_ptr(), idx.data_ptr(), g_sel.data_ptr(),
                          u_sel.data_ptr(), _lib.ptr(s_sel), _lib.ptr(z_sel), dx.data_ptr(), d_gate.data_ptr(),
                          d_up.data_ptr(), d_down.data_ptr(), ws.data_ptr(), ws_bytes, evs[0], evs[1], evs[2],
                          _lib.stream_ptr(dev))
@@ -144,9 +144,12 @@ class _MoCB200Function(torch.autograd.Function):
     """Autograd node of the MoC FFN; stands where _MoCFunction / _MoCGCPFunction / _MoC28Function
     stand in the reference (moc/ffn.py:124-259, :262-310, :372-497).
 
-    Saved for backward: x, the selection bitmap with per-word ranks, g_sel, u_sel and - unless
-    the mode is moc_gcp - s_sel, z_sel: the compact [tokens, k] activation layout of
-    moc/ffn.py:166-169 / :417, never a dense [tokens, d_ffn] tensor.
+    Saved for backward: x, the selected channel indices (int16), g_sel and u_sel: the compact
+    [tokens, k] activation layout of moc/ffn.py:417, never a dense [tokens, d_ffn] tensor. The
+    reference's `moc` mode additionally keeps s_sel = SiLU(g_sel) and z_sel = s_sel * u_sel
+    (moc/ffn.py:166-169) to skip their recomputation; here the backward kernels rebuild both
+    bit-identically inside their own passes at no extra cost, so `moc` and `moc_gcp` share the
+    smaller saved set unless ``materialize_sz`` asks for the reference's one.
     """
 
     @staticmethod
@@ -165,7 +168,7 @@ class _MoCB200Function(torch.autograd.Function):
             down_w_t = transpose_weight(down_w.detach().to(compute_dtype))
         y, idx, g_sel, u_sel, s_sel, z_sel, bitmap, rank0 = moc_ffn_forward(
             x2d, gw, uw, down_w_t, k, select, save_sz=not recompute_sz)
-        saved = [x2d, gw, uw, down_w_t, bitmap, rank0, g_sel, u_sel]
+        saved = [x2d, gw, uw, down_w_t, idx, g_sel, u_sel]
         if not recompute_sz:
             saved += [s_sel, z_sel]
         ctx.save_for_backward(*saved)
@@ -179,8 +182,8 @@ class _MoCB200Function(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out, _grad_idx):
         saved = ctx.saved_tensors
-        x2d, gw, uw, down_w_t, bitmap, rank0, g_sel, u_sel = saved[:8]
-        s_sel, z_sel = (None, None) if ctx.recompute_sz else saved[8:10]
+        x2d, gw, uw, down_w_t, idx, g_sel, u_sel = saved[:7]
+        s_sel, z_sel = (None, None) if ctx.recompute_sz else saved[7:9]
         go = grad_out.reshape(-1, grad_out.shape[-1]).to(x2d.dtype).contiguous()
         hook = _grad_ready_hook
         events = None
@@ -188,7 +191,7 @@ class _MoCB200Function(torch.autograd.Function):
             events = tuple(torch.cuda.Event() for _ in range(3))
             for ev in events:
                 ev.record()   # PyTorch creates the CUDA event lazily; the library re-records it
-        dx, d_gate, d_up, d_down = moc_ffn_backward(go, x2d, gw, uw, down_w_t, bitmap, rank0, g_sel, u_sel, s_sel,
+        dx, d_gate, d_up, d_down = moc_ffn_backward(go, x2d, gw, uw, down_w_t, idx, g_sel, u_sel, s_sel,
                                                     z_sel, events)
         d_gate = d_gate.to(ctx.w_dtypes[0])
         d_up = d_up.to(ctx.w_dtypes[1])
@@ -265,6 +268,8 @@ class MoCSwiGLUFFN(nn.Module):
         self._down_weight_t: torch.Tensor | None = None
         self._down_weight_t_key = None
         self.last_topk_idx: torch.Tensor | None = None
+        # True: also write and keep s_sel, z_sel like the reference's `moc` mode (moc/ffn.py:166-169)
+        self.materialize_sz = False
 
     def _ensure_down_weight_t(self, dtype: torch.dtype) -> torch.Tensor:
         w = self.down_proj.weight
@@ -289,7 +294,7 @@ class MoCSwiGLUFFN(nn.Module):
             down_w_t,
             self.k,
             select,
-            self.mode.startswith("moc_gcp"),
+            not self.materialize_sz,
         )
         self.last_topk_idx = idx
         return y

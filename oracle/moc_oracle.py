@@ -88,10 +88,10 @@ def effective_k_2of8(inter: int) -> int:
 
 
 def selection_bitmap(idx: torch.Tensor, inter: int) -> np.ndarray:
-    """uint32 mask words [rows, ceil64(inter)/32] of a selected index set (layout of the CUDA
+    """uint32 mask words [rows, ceil128(inter)/32] of a selected index set (layout of the CUDA
     kernels' bitmap output; no counterpart in the reference, which keeps indices only)."""
     rows = idx.reshape(-1, idx.shape[-1]).numpy()
-    words = (inter + 63) // 64 * 2
+    words = (inter + 127) // 128 * 4
     out = np.zeros((rows.shape[0], words), dtype=np.uint32)
     r = np.repeat(np.arange(rows.shape[0]), rows.shape[1])
     c = rows.reshape(-1)
