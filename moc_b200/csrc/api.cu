@@ -91,7 +91,7 @@ int64_t moc_mask_words(int64_t d_ffn) { return mask_words(d_ffn); }
 int64_t moc_select_2of8_k(int64_t d_ffn) { return (d_ffn / 8) * 2 + (d_ffn % 8 < 2 ? d_ffn % 8 : 2); }
 
 int64_t moc_ffn_fwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
-  return kStatusBytes + round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
+  return kStatusBytes + 2 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
 }
 int64_t moc_ffn_bwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
   return kStatusBytes + 3 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
@@ -197,20 +197,20 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
     rc = launch_select_2of8(dtype, dense, ld, (int)tokens, (int)d_ffn, 1, idx, g_sel, bitmap, rank0, stream);
   if (rc != kOk) return rc;
 
-  // U = X Wu^T with the selected-activation epilogue; S' is overwritten by Z' (moc/ffn.py:146-161)
+  // U = X Wu^T; the epilogue turns S' into Z' = S' * U in place and keeps the rounded U row (moc/ffn.py:146-161)
+  void* u_dense = static_cast<uint8_t*>(dense) + round_up_i64(tokens * ld * (int64_t)esize(dtype), 256);
   p.b[0] = operand(w_up, d, 0);
   p.epi = EpiArgs{};
-  p.epi.kind = kEpiUpSparse;
+  p.epi.kind = kEpiUpGated;
   p.epi.dense0 = dense;
+  p.epi.dense1 = u_dense;
   p.epi.ld_dense = ld;
-  p.epi.bitmap = bitmap;
-  p.epi.rank0 = rank0;
-  p.epi.words = words;
-  p.epi.k_sel = (int)k;
-  p.epi.u_sel = u_sel;
-  p.epi.s_sel = s_sel;
-  p.epi.z_sel = z_sel;
   if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+
+  // compact saved set: the selected channels of U (and, on request, s and z) (moc/ffn.py:156, :166-169)
+  if ((rc = launch_gather_sel(dtype, idx, u_dense, dense, g_sel, u_sel, s_sel, z_sel, ld, (int)tokens, (int)k,
+                              stream)) != kOk)
+    return rc;
 
   // Y = Z' Wd^T (moc/ffn.py:163): A = Z' [tokens, F] K-major, B = W_down^T [F, d] N-contiguous
   GemmProblem q = problem(dtype, status, tokens, d, d_ffn);

@@ -40,6 +40,18 @@ template <> struct Num<__nv_bfloat16> {
   __device__ __forceinline__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
   // value after a round trip through the storage type
   __device__ __forceinline__ static float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+  // storage value of a float that is already exactly representable (no conversion instruction)
+  __device__ __forceinline__ static __nv_bfloat16 from_rounded(float v) {
+    const uint16_t b = static_cast<uint16_t>(__float_as_uint(v) >> 16);
+    return *reinterpret_cast<const __nv_bfloat16*>(&b);
+  }
+  // rounds two values with one packed conversion (the scalar conversion runs on the slow XU pipe)
+  __device__ __forceinline__ static void round_pair(float& a, float& b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+    a = __uint_as_float(w << 16);
+    b = __uint_as_float(w & 0xFFFF0000u);
+  }
 };
 
 template <> struct Num<float> {
@@ -47,6 +59,8 @@ template <> struct Num<float> {
   __device__ __forceinline__ static float to_float(float v) { return v; }
   __device__ __forceinline__ static float from_float(float v) { return v; }
   __device__ __forceinline__ static float round(float v) { return v; }
+  __device__ __forceinline__ static float from_rounded(float v) { return v; }
+  __device__ __forceinline__ static void round_pair(float&, float&) {}
 };
 
 // Sigmoid evaluated in fp32 (SiLU(g) = g * sigmoid(g), moc/training/triton_sparse_aux.py:39).

@@ -11,9 +11,11 @@
 // with col0 % 32 == 0, row < M, col0 < N, nchunks <= 4, and acc zero for columns >= N.
 // `group` is the problem index of a grouped launch (0 otherwise).
 //
-// The sparse forward epilogue is where the MoC-specific work is fused into the up-projection
-// GEMM; it replaces sparse_forward_aux of the reference
-// (moc/training/triton_sparse_aux.py:17-49, :197-231) and never writes a full U to HBM.
+// Epilogues are kept to dense, branch-free, vectorised work: an epilogue warp is a serial
+// instruction stream next to the tensor pipe, and measured on B200 every per-element branch,
+// scalar f32->bf16 conversion (XU pipe) or 2-byte store in it shows up one-to-one in the GEMM's
+// duration. All index-dependent work (gather / scatter by selected channel) is done by the
+// row kernels in kernels.cu.
 #pragma once
 
 #include "common.cuh"
@@ -45,6 +47,7 @@ template <> struct Chunk32<__nv_bfloat16> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) q[i] = s[i];
   }
+  // rounds to nearest even with packed conversions
   __device__ __forceinline__ static void store(__nv_bfloat16* p, const float (&v)[32]) {
     uint4* q = reinterpret_cast<uint4*>(p);
 #pragma unroll
@@ -55,6 +58,18 @@ template <> struct Chunk32<__nv_bfloat16> {
         const __nv_bfloat162 h = __floats2bfloat162_rn(v[i * 8 + 2 * j], v[i * 8 + 2 * j + 1]);
         a[j] = *reinterpret_cast<const uint32_t*>(&h);
       }
+      q[i] = make_uint4(a[0], a[1], a[2], a[3]);
+    }
+  }
+  // values already representable in bf16: pure bit packing, no conversion instruction
+  __device__ __forceinline__ static void store_rounded(__nv_bfloat16* p, const float (&v)[32]) {
+    uint4* q = reinterpret_cast<uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t a[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        a[j] = (__float_as_uint(v[i * 8 + 2 * j]) >> 16) | (__float_as_uint(v[i * 8 + 2 * j + 1]) & 0xFFFF0000u);
       q[i] = make_uint4(a[0], a[1], a[2], a[3]);
     }
   }
@@ -81,14 +96,8 @@ template <> struct Chunk32<float> {
 #pragma unroll
     for (int i = 0; i < 8; ++i) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   }
+  __device__ __forceinline__ static void store_rounded(float* p, const float (&v)[32]) { store(p, v); }
 };
-
-template <typename T>
-__device__ __forceinline__ void chunk_load(const T* p, float (&v)[32]) {
-  uint4 q[Chunk32<T>::kVecs];
-  Chunk32<T>::load_raw(p, q);
-  Chunk32<T>::unpack(q, v);
-}
 
 // ---- plain store: C[row, col] (or C[col, row] when transposed), one C per group ------------
 template <typename T>
@@ -124,74 +133,40 @@ struct EpiStore {
   }
 };
 
-// ---- forward: up projection -> selected activations -------------------------------------
+// ---- forward: up projection x selected SiLU(gate) ------------------------------------------
 // acc = U tile. The selection kernel has already replaced the dense gate row by
-// S' = mask * round(SiLU(G)) (zero outside the selected channels, moc/ffn.py:157), so the
-// epilogue is branch-free dense math: u = round(U), z = round(S' * u) (moc/ffn.py:158),
-// written over the S' chunk in place as the zero-filled Z' chunk that the down projection
-// consumes (moc/ffn.py:160-163). The selected u (and on request s, z) also go to the
-// compact per-token arrays at the channel's rank (moc/ffn.py:156, :166-169). Mask words and
-// ranks of the whole run are fetched in begin(); the S' chunk is fetched in prefetch(),
-// while the accumulator load is in flight.
+// S' = mask * round(SiLU(G)) (zero outside the selected channels, moc/ffn.py:157). The epilogue
+// rounds u = round(U) (the reference's U is a stored tensor, moc/ffn.py:146), writes
+// z = round(S' * u) over the S' chunk in place - the zero-filled Z' that the down projection
+// consumes (moc/ffn.py:158-163) - and the dense u row to a second scratch matrix, from which
+// gather_sel_kernel picks the selected channels into the compact saved set (moc/ffn.py:156).
 template <typename T>
-struct EpiUpSparse {
+struct EpiUpGated {
   struct Ctx {
-    uint32_t word[kEpiMaxChunks];
-    uint32_t rank[kEpiMaxChunks];
     uint4 s[Chunk32<T>::kVecs];
   };
-  T* sz;                    // in: S' [tokens, ld]; out: Z' [tokens, ld]
+  T* sz;        // in: S' [tokens, ld]; out: Z' [tokens, ld]
+  T* u_out;     // out: round(U) [tokens, ld]
   int64_t ld;
-  const uint32_t* bitmap;   // [tokens, words], words % 4 == 0
-  const uint16_t* rank0;    // [tokens, words] rank of the first channel of each word
-  int words;
-  int k;
-  T* u_sel;                 // [tokens, k]
-  T* s_sel;                 // [tokens, k] or null
-  T* z_sel;                 // [tokens, k] or null
 
-  __device__ __forceinline__ void begin(Ctx& ctx, int, int row, int col_first, int nchunks) const {
-    const int w0 = col_first >> 5;
-    const uint32_t* bw = bitmap + static_cast<int64_t>(row) * words + w0;
-    const uint16_t* rk = rank0 + static_cast<int64_t>(row) * words + w0;
-    if ((w0 & 3) == 0) {   // aligned run of four words: one 16-byte and one 8-byte load
-      const uint4 b = *reinterpret_cast<const uint4*>(bw);
-      const uint2 r = *reinterpret_cast<const uint2*>(rk);
-      ctx.word[0] = b.x; ctx.word[1] = b.y; ctx.word[2] = b.z; ctx.word[3] = b.w;
-      ctx.rank[0] = r.x & 0xFFFFu; ctx.rank[1] = r.x >> 16; ctx.rank[2] = r.y & 0xFFFFu; ctx.rank[3] = r.y >> 16;
-    } else {
-#pragma unroll
-      for (int c = 0; c < kEpiMaxChunks; ++c) {
-        ctx.word[c] = (c < nchunks) ? bw[c] : 0u;
-        ctx.rank[c] = (c < nchunks) ? rk[c] : 0u;
-      }
-    }
+  __device__ __forceinline__ void begin(Ctx&, int, int, int, int) const {}
+  __device__ __forceinline__ void prefetch(Ctx& ctx, int row, int col0, int) const {
+    Chunk32<T>::load_raw(sz + static_cast<int64_t>(row) * ld + col0, ctx.s);
   }
-  __device__ __forceinline__ void prefetch(Ctx& ctx, int row, int col0, int c) const {
-    if (ctx.word[c] != 0u) Chunk32<T>::load_raw(sz + static_cast<int64_t>(row) * ld + col0, ctx.s);
-  }
-  __device__ __forceinline__ void operator()(Ctx& ctx, int, int row, int col0, int c, const float (&acc)[32]) const {
-    const uint32_t word = ctx.word[c];
-    T* chunk = sz + static_cast<int64_t>(row) * ld + col0;
-    if (word == 0u) return;   // the S' chunk is all zero already and stays the Z' chunk
-    float s[32], out[32];
+  __device__ __forceinline__ void operator()(Ctx& ctx, int, int row, int col0, int, const float (&acc)[32]) const {
+    float s[32], u[32], out[32];
     Chunk32<T>::unpack(ctx.s, s);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) out[j] = Num<T>::round(s[j] * Num<T>::round(acc[j]));
-    Chunk32<T>::store(chunk, out);
-    T* up = u_sel + static_cast<int64_t>(row) * k + ctx.rank[c];
-    T* sp = s_sel ? s_sel + static_cast<int64_t>(row) * k + ctx.rank[c] : nullptr;
-    T* zp = z_sel ? z_sel + static_cast<int64_t>(row) * k + ctx.rank[c] : nullptr;
-    int pos = 0;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if ((word >> j) & 1u) {
-        up[pos] = Num<T>::from_float(acc[j]);
-        if (sp) sp[pos] = Num<T>::from_float(s[j]);
-        if (zp) zp[pos] = Num<T>::from_float(out[j]);
-        ++pos;
-      }
+    for (int j = 0; j < 32; j += 2) {
+      u[j] = acc[j];
+      u[j + 1] = acc[j + 1];
+      Num<T>::round_pair(u[j], u[j + 1]);
+      out[j] = s[j] * u[j];
+      out[j + 1] = s[j + 1] * u[j + 1];
     }
+    const int64_t off = static_cast<int64_t>(row) * ld + col0;
+    Chunk32<T>::store_rounded(u_out + off, u);
+    Chunk32<T>::store(sz + off, out);   // the packed store conversion is the rounding of z
   }
 };
 
@@ -215,13 +190,18 @@ struct EpiDenseSwiGLU {
     float gv[32], out[32], u[32];
     Chunk32<T>::unpack(ctx.g, gv);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      u[j] = Num<T>::round(acc[j]);
-      float s;
-      moc_fwd_point<T>(gv[j], u[j], s, out[j]);
+    for (int j = 0; j < 32; j += 2) {
+      u[j] = acc[j];
+      u[j + 1] = acc[j + 1];
+      Num<T>::round_pair(u[j], u[j + 1]);
+      float s0 = gv[j] * sigmoid_act<T>(gv[j]), s1 = gv[j + 1] * sigmoid_act<T>(gv[j + 1]);
+      Num<T>::round_pair(s0, s1);
+      out[j] = s0 * u[j];
+      out[j + 1] = s1 * u[j + 1];
     }
-    Chunk32<T>::store(u_out + static_cast<int64_t>(row) * ld + col0, u);
-    Chunk32<T>::store(z_out + static_cast<int64_t>(row) * ld + col0, out);
+    const int64_t off = static_cast<int64_t>(row) * ld + col0;
+    Chunk32<T>::store_rounded(u_out + off, u);
+    Chunk32<T>::store(z_out + off, out);
   }
 };
 

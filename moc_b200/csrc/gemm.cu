@@ -238,22 +238,15 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
       epi.n = p.n;
       return run(epi);
     }
-    case kEpiUpSparse: {
-      if (!dense_ok || e.words % 4 != 0 || !aligned16(e.bitmap) || (reinterpret_cast<uintptr_t>(e.rank0) & 7u)) {
-        set_error("dense scratch / mask arrays must be 16-byte aligned with a leading dimension that is a "
-                  "multiple of 128");
+    case kEpiUpGated: {
+      if (!dense_ok || !e.dense0 || !e.dense1) {
+        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 128");
         return kErrWorkspace;
       }
-      EpiUpSparse<T> epi;
+      EpiUpGated<T> epi;
       epi.sz = static_cast<T*>(e.dense0);
+      epi.u_out = static_cast<T*>(e.dense1);
       epi.ld = e.ld_dense;
-      epi.bitmap = e.bitmap;
-      epi.rank0 = e.rank0;
-      epi.words = e.words;
-      epi.k = e.k_sel;
-      epi.u_sel = static_cast<T*>(e.u_sel);
-      epi.s_sel = static_cast<T*>(e.s_sel);
-      epi.z_sel = static_cast<T*>(e.z_sel);
       return run(epi);
     }
     case kEpiDenseSwiGLU: {

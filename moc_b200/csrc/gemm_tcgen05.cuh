@@ -4,9 +4,9 @@
 //   * persistent: one CTA per SM walks output tiles of 128 x 256;
 //   * warp 0 = TMA producer (4-stage ring of 128-byte-swizzled A/B tiles, BLOCK_K = 64),
 //     warp 1 = tcgen05.mma issuer (one elected thread; also owns the TMEM allocation),
-//     warps 2-9 = epilogue: two warps per 32-lane TMEM quadrant, each taking one 128-column
-//     half of the tile, so that global-memory latency in a fused epilogue is covered by a
-//     second warp on the same scheduler;
+//     warps 2-17 = epilogue: four warps per 32-lane TMEM quadrant, each taking one 64-column
+//     slice of the tile; a fused epilogue is a serial chain of dependent instructions per
+//     warp, so its latency is hidden by warps, not by instruction-level parallelism;
 //   * two 256-column TMEM accumulators, so the epilogue of tile i overlaps the MMAs of
 //     tile i + 1;
 //   * both operands may be K-major (K contiguous in memory) or MN-major (M/N contiguous),
@@ -40,7 +40,9 @@ constexpr int kTileBBytes = kBlockN * kBlockK * 2;   // 32 KiB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
 constexpr int kMnBoxBytes = 64 * kBlockK * 2;        // one MN-major TMA box: 64 (mn) x 64 (k)
 constexpr int kTmemCols = 512;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;
+constexpr int kEpiParts = kEpiWarps / 4;              // column slices of a tile, one per warp of a quadrant
+constexpr int kEpiPartCols = kBlockN / kEpiParts;
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -201,8 +203,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quad = warp & 3;              // TMEM lanes [32*quad, 32*quad+32) belong to this warp
-    const int half = (warp - 2) >> 2;       // which 128-column half of the tile
-    constexpr int kChunks = kBlockN / 2 / 32;
+    const int part = (warp - 2) >> 2;       // which column slice of the tile
+    constexpr int kChunks = kEpiPartCols / 32;
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       const uint32_t acc = tcount & 1u;
@@ -210,7 +212,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
       const int group = tile / tiles_per_group;
       const int t = tile - group * tiles_per_group;
       const int m0 = (t / sh.tiles_n) * kBlockM;
-      const int col_first = (t % sh.tiles_n) * kBlockN + half * (kBlockN / 2);
+      const int col_first = (t % sh.tiles_n) * kBlockN + part * kEpiPartCols;
       const int row = m0 + quad * 32 + lane;
       const int nchunks = min(kChunks, (sh.n - col_first + 31) / 32);   // <= 0: nothing to do
       const bool active = row < sh.m && nchunks > 0;
@@ -223,7 +225,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
       }
       ptx::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBlockN +
-                             half * (kBlockN / 2);
+                             part * kEpiPartCols;
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
         if (c < nchunks) {   // warp-uniform

@@ -14,7 +14,7 @@ struct MatOperand {
   int mn_major;   // 0: memory is [mn][k] (K contiguous); 1: memory is [k][mn] (M/N contiguous)
 };
 
-enum EpiKind : int { kEpiStore = 0, kEpiUpSparse = 1, kEpiDenseSwiGLU = 2 };
+enum EpiKind : int { kEpiStore = 0, kEpiUpGated = 1, kEpiDenseSwiGLU = 2 };
 
 constexpr int kGemmMaxGroups = 3;
 
@@ -24,18 +24,12 @@ struct EpiArgs {
   void* c[kGemmMaxGroups];
   int64_t ldc[kGemmMaxGroups];
   int transposed[kGemmMaxGroups];
-  // kEpiUpSparse: dense0 = G -> Z' in place. kEpiDenseSwiGLU: dense0 = G (in), dense1 = U (out), dense2 = Z (out)
+  // kEpiUpGated: dense0 = S' -> Z' in place, dense1 = U (out).
+  // kEpiDenseSwiGLU: dense0 = G (in), dense1 = U (out), dense2 = Z (out)
   void* dense0;
   void* dense1;
   void* dense2;
   int64_t ld_dense;
-  const uint32_t* bitmap;
-  const uint16_t* rank0;
-  int words;
-  int k_sel;
-  void* u_sel;
-  void* s_sel;
-  void* z_sel;
 };
 
 // C_g[m, n] = A_g[m, k0] * B_g[n, k0]^T for g < groups, or, with groups == 1 and k1 > 0,
@@ -63,6 +57,10 @@ int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
 // Z'[tokens, ld] <- zero-filled scatter of the compact z (or of round(round(SiLU(g)) * u) when z_sel is null)
 int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void* g_sel, const void* u_sel, void* dense,
                     int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
+// compact saved set from dense rows: u_sel[t, p] = u_dense[t, idx[t, p]]; optional s_sel = round(SiLU(g_sel)),
+// z_sel[t, p] = z_dense[t, idx[t, p]]
+int launch_gather_sel(int dtype, const int16_t* idx, const void* u_dense, const void* z_dense, const void* g_sel,
+                      void* u_sel, void* s_sel, void* z_sel, int64_t ld, int tokens, int k, cudaStream_t stream);
 // dZ[tokens, ld] (in) -> dG' (grad_g_out) and dU' (written over dZ in place): gather, SiLU', zero fill
 int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
                       void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
@@ -77,7 +75,7 @@ int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_
 enum ProfTag : int {
   kProfEnd = 0, kProfGemmTc = 1, kProfGemmSimt = 2, kProfTopk = 3, kProfSel2of8 = 4, kProfExpand = 5,
   kProfTranspose = 6, kProfDecodeGate = 7, kProfDecodeUp = 8, kProfDecodeDown = 9, kProfDecodeFused28 = 10,
-  kProfDecodeDense = 11, kProfBwdSparse = 12,
+  kProfDecodeDense = 11, kProfBwdSparse = 12, kProfGatherSel = 13,
 };
 void prof_mark(int tag, cudaStream_t stream);
 

@@ -468,6 +468,32 @@ expand_z_kernel(const int16_t* __restrict__ idx, const T* __restrict__ z_sel, co
   row_store(zrow, dense + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
 }
 
+// Compact saved set of the forward pass: u_sel[p] = U[token, idx[p]] from the dense rounded U row;
+// on request s_sel[p] = round(SiLU(g_sel[p])) and z_sel[p] = Z'[token, idx[p]] (moc/ffn.py:156-158).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+gather_sel_kernel(const int16_t* __restrict__ idx, const T* __restrict__ u_dense, const T* __restrict__ z_dense,
+                  const T* __restrict__ g_sel, T* __restrict__ u_sel, T* __restrict__ s_sel, T* __restrict__ z_sel,
+                  int64_t ld, int k) {
+  extern __shared__ __align__(16) uint8_t row_smem[];
+  T* urow = reinterpret_cast<T*>(row_smem);
+  const int row = blockIdx.x;
+  const int64_t crow = static_cast<int64_t>(row) * k;
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(u_dense + static_cast<int64_t>(row) * ld);
+    uint4* dst = reinterpret_cast<uint4*>(urow);
+    const int nvec = static_cast<int>(ld) * static_cast<int>(sizeof(T)) / 16;
+    for (int v = threadIdx.x; v < nvec; v += kRowThreads) dst[v] = src[v];
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < k; p += kRowThreads) {
+    const int ch = idx[crow + p];
+    u_sel[crow + p] = urow[ch];
+    if (s_sel) s_sel[crow + p] = Num<T>::from_float(silu_round<T>(Num<T>::to_float(g_sel[crow + p])));
+    if (z_sel) z_sel[crow + p] = z_dense[static_cast<int64_t>(row) * ld + ch];
+  }
+}
+
 // dZ (dense, rounded GEMM output) -> dG', dU' (dense, zero outside the selected channels).
 // dU' overwrites dZ in place, dG' goes to its own buffer.
 // gz = dZ, grad_s = round(u * gz), grad_u = round(s * gz), grad_g = round(grad_s * SiLU'(g)), with
@@ -604,6 +630,30 @@ int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void
                                                               static_cast<T*>(dense), ld, k);
   }
   return check_last("expand_z");
+}
+
+int launch_gather_sel(int dtype, const int16_t* idx, const void* u_dense, const void* z_dense, const void* g_sel,
+                      void* u_sel, void* s_sel, void* z_sel, int64_t ld, int tokens, int k, cudaStream_t stream) {
+  if (tokens == 0) return kOk;
+  int rc;
+  if (dtype == kBF16) {
+    using T = __nv_bfloat16;
+    const size_t smem = ld * sizeof(T);
+    if ((rc = row_smem_setup<T>(gather_sel_kernel<T>, smem, "gather_sel")) != kOk) return rc;
+    prof_mark(kProfGatherSel, stream);
+    gather_sel_kernel<T><<<tokens, kRowThreads, smem, stream>>>(
+        idx, static_cast<const T*>(u_dense), static_cast<const T*>(z_dense), static_cast<const T*>(g_sel),
+        static_cast<T*>(u_sel), static_cast<T*>(s_sel), static_cast<T*>(z_sel), ld, k);
+  } else {
+    using T = float;
+    const size_t smem = ld * sizeof(T);
+    if ((rc = row_smem_setup<T>(gather_sel_kernel<T>, smem, "gather_sel")) != kOk) return rc;
+    prof_mark(kProfGatherSel, stream);
+    gather_sel_kernel<T><<<tokens, kRowThreads, smem, stream>>>(
+        idx, static_cast<const T*>(u_dense), static_cast<const T*>(z_dense), static_cast<const T*>(g_sel),
+        static_cast<T*>(u_sel), static_cast<T*>(s_sel), static_cast<T*>(z_sel), ld, k);
+  }
+  return check_last("gather_sel");
 }
 
 int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
