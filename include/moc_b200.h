@@ -119,6 +119,64 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
                 void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
                 int64_t workspace_bytes, void* ev_down, void* ev_gate, void* ev_up, void* stream);
 
+/* Dense SwiGLU FFN forward y = (SiLU(x Wg^T) * (x Wu^T)) Wd^T on the same GEMM core, the comparison
+ * row of the reference (StandardSwiGLUFFN.forward, moc/ffn.py:111-121: three nn.Linear calls).
+ * g_out, u_out [tokens, moc_ffn_ld(d_ffn)] receive the rounded gate / up activations, which the
+ * backward pass needs (what autograd saves for the reference). Workspace as for moc_ffn_fwd. */
+int moc_dense_ffn_fwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const void* x, const void* w_gate,
+                      const void* w_up, const void* w_down_t, void* y, void* g_out, void* u_out, void* workspace,
+                      int64_t workspace_bytes, void* stream);
+
+/* Dense SwiGLU FFN backward (PyTorch autograd of moc/ffn.py:120-121). g, u: the forward pass's outputs.
+ * Gradients are overwritten; grad_w_down has the parameter layout [d, d_ffn]. Workspace as for moc_ffn_bwd. */
+int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const void* grad_y, const void* x,
+                      const void* w_gate, const void* w_up, const void* w_down_t, const void* g, const void* u,
+                      void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
+                      int64_t workspace_bytes, void* stream);
+
+/* ---- decode path: a few token rows at a time, bf16 only (like the reference's fast paths,
+ * moc/inference/cuda/optimized_global_moc_ext.cpp:67-74). x[batch, d], w_gate / w_up [d_ffn, d],
+ * w_down_t[d_ffn, d] = W_down^T (the reference keeps the same copy, inference_ffn.py:104-110),
+ * y[batch, d]. d % 8 == 0. All scratch (gate scores, indices, sparse z, split-K partial sums) lives in
+ * `workspace` (moc_decode_workspace_bytes, 256-byte aligned); nothing is allocated. The launches are
+ * stream-ordered and capturable in a CUDA graph. Results are deterministic (no floating-point
+ * atomics). ---- */
+int64_t moc_decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn);
+
+/* Global MoC decode FFN: gate projection, row-wise Top-K (lowest index wins ties), SiLU(g) * (x . W_up
+ * rows of the selected channels), gathered down projection. Replaces
+ * InferenceMoCSwiGLUFFN.moc_inference_optimized_global_after_gate_native (inference_ffn.py:182-196:
+ * gate_proj + moc_native::optimized_global_after_gate_bf16) and equals masked_reference
+ * (inference_ffn.py:169-180) up to bf16 rounding. */
+int moc_decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, const void* x, const void* w_gate,
+                      const void* w_up, const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes,
+                      void* stream);
+
+/* Same with the gate scores supplied by the caller (gate_scores[batch, d_ffn], contiguous): the exact
+ * counterpart of moc_native::optimized_global_after_gate_bf16(x, gate_scores, up_weight, down_weight_t, k)
+ * (optimized_global_moc_ext.cpp:61-76, .cu:457-540). */
+int moc_decode_after_gate(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, const void* x, const void* gate_scores,
+                          const void* w_up, const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes,
+                          void* stream);
+
+/* MoC 2:8 decode FFN: top-2 of every 8 consecutive gate channels (tail group: top-min(2, tail)), selection on
+ * the bf16-rounded gate. Replaces moc::fused_grouped_top2_up_silu + moc::selected_grouped_down
+ * (moc/inference/triton_grouped_moc_ops.py:26-131, triton_fused_ffn_kernels.py:30-156, :229-267); unlike
+ * them it accepts d_ffn % 8 != 0. */
+int moc_decode_2of8(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
+                    const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Dense SwiGLU decode FFN (InferenceMoCSwiGLUFFN.dense_baseline, inference_ffn.py:164-167). */
+int moc_decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
+                     const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* y[b, :] = sum_k sparse_z[b, k] * w_down_t[idx[b, k], :]: the gathered down projection alone
+ * (moc_native::optimized_global_selected_down_bf16, optimized_global_moc_ext.cu:247-372, and
+ * moc::selected_grouped_down, triton_grouped_moc_ops.py:96-131), with int16 indices. */
+int moc_decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* sparse_z,
+                             const int16_t* idx, const void* w_down_t, void* y, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+
 /* Per-kernel timing without a profiler. Between moc_profile_begin and moc_profile_end (process-wide,
  * one profile at a time) the library records events[0], events[1], ... (a HOST array of created
  * cudaEvent_t handles, timing enabled) on the stream of each call, one right before every

@@ -39,16 +39,14 @@ SIGNATURES = {
     "moc_profile_begin": (c_int, [_P, c_int]),
     "moc_profile_end": (c_int, [_P, c_int]),
     "moc_read_status": (c_int, [_P, _P]),
-    "moc_dense_ffn_fwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 7 + [c_int64, _P]),
+    "moc_dense_ffn_fwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 8 + [c_int64, _P]),
     "moc_dense_ffn_bwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 12 + [c_int64, _P]),
     "moc_decode_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
-    "moc_decode_global": (c_int, [c_int64, c_int64, c_int64, c_int64] + [_P] * 7 + [c_int64, _P]),
-    "moc_decode_2of8": (c_int, [c_int64, c_int64, c_int64] + [_P] * 7 + [c_int64, _P]),
-    "moc_decode_dense": (c_int, [c_int64, c_int64, c_int64] + [_P] * 6 + [c_int64, _P]),
-    "moc_decode_selected_down": (c_int, [c_int64, c_int64, c_int64, c_int64] + [_P] * 4 + [_P]),
-    "moc_decode_global_static": (c_int, [c_int64, c_int64, c_int64, c_int64] + [_P] * 6 + [_P]),
-    "moc_decode_static_max_batch": (c_int64, []),
-    "moc_decode_static_max_d_ffn": (c_int64, []),
+    "moc_decode_global": (c_int, [c_int64] * 4 + [_P] * 6 + [c_int64, _P]),
+    "moc_decode_after_gate": (c_int, [c_int64] * 4 + [_P] * 6 + [c_int64, _P]),
+    "moc_decode_2of8": (c_int, [c_int64] * 3 + [_P] * 6 + [c_int64, _P]),
+    "moc_decode_dense": (c_int, [c_int64] * 3 + [_P] * 6 + [c_int64, _P]),
+    "moc_decode_selected_down": (c_int, [c_int64] * 4 + [_P] * 5 + [c_int64, _P]),
 }
 
 _lib = None

@@ -318,6 +318,176 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   return rc;
 }
 
+int moc_dense_ffn_fwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const void* x, const void* w_gate,
+                      const void* w_up, const void* w_down_t, void* y, void* g_out, void* u_out, void* workspace,
+                      int64_t workspace_bytes, void* stream_) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  int rc = check_dims(tokens, d, d_ffn, 1);
+  if (rc != kOk) return rc;
+  if (!x || !w_gate || !w_up || !w_down_t || !y || !g_out || !u_out || !workspace) {
+    set_error("moc_dense_ffn_fwd: null pointer");
+    return kErrInvalidArg;
+  }
+  if (workspace_bytes < moc_ffn_fwd_workspace_bytes(dtype, tokens, d_ffn) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    set_error("moc_dense_ffn_fwd: workspace too small or not 256-byte aligned");
+    return kErrWorkspace;
+  }
+  cudaStream_t stream = as_stream(stream_);
+  int* status = static_cast<int*>(workspace);
+  if (cudaMemsetAsync(status, 0, kStatusBytes, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
+  if (tokens == 0) return kOk;
+  void* z = static_cast<uint8_t*>(workspace) + kStatusBytes;
+  const int64_t ld = ffn_ld(d_ffn);
+  // G = X Wg^T, then U = X Wu^T with Z = SiLU(G) * U in the epilogue, then Y = Z Wd^T (moc/ffn.py:120-121)
+  GemmProblem p = problem(dtype, status, tokens, d_ffn, d);
+  p.a[0] = operand(x, d, 0);
+  p.b[0] = operand(w_gate, d, 0);
+  p.epi = store_epi(g_out, ld, 0);
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+  p.b[0] = operand(w_up, d, 0);
+  p.epi = EpiArgs{};
+  p.epi.kind = kEpiDenseSwiGLU;
+  p.epi.dense0 = g_out;
+  p.epi.dense1 = u_out;
+  p.epi.dense2 = z;
+  p.epi.ld_dense = ld;
+  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
+  GemmProblem q = problem(dtype, status, tokens, d, d_ffn);
+  q.a[0] = operand(z, ld, 0);
+  q.b[0] = operand(w_down_t, d, 1);
+  q.epi = store_epi(y, d, 0);
+  rc = launch_gemm(q, stream);
+  prof_mark(kProfEnd, stream);
+  return rc;
+}
+
+int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const void* grad_y, const void* x,
+                      const void* w_gate, const void* w_up, const void* w_down_t, const void* g, const void* u,
+                      void* grad_x, void* grad_w_gate, void* grad_w_up, void* grad_w_down, void* workspace,
+                      int64_t workspace_bytes, void* stream_) {
+  if (bad_dtype(dtype)) return kErrInvalidArg;
+  int rc = check_dims(tokens, d, d_ffn, 1);
+  if (rc != kOk) return rc;
+  if (!grad_y || !x || !w_gate || !w_up || !w_down_t || !g || !u || !grad_x || !grad_w_gate || !grad_w_up ||
+      !grad_w_down || !workspace) {
+    set_error("moc_dense_ffn_bwd: null pointer");
+    return kErrInvalidArg;
+  }
+  if (workspace_bytes < moc_ffn_bwd_workspace_bytes(dtype, tokens, d_ffn) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    set_error("moc_dense_ffn_bwd: workspace too small or not 256-byte aligned");
+    return kErrWorkspace;
+  }
+  cudaStream_t stream = as_stream(stream_);
+  int* status = static_cast<int*>(workspace);
+  if (cudaMemsetAsync(status, 0, kStatusBytes, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
+  const size_t es = esize(dtype);
+  if (tokens == 0) {
+    if (cudaMemsetAsync(grad_w_gate, 0, (size_t)d_ffn * d * es, stream) != cudaSuccess ||
+        cudaMemsetAsync(grad_w_up, 0, (size_t)d_ffn * d * es, stream) != cudaSuccess ||
+        cudaMemsetAsync(grad_w_down, 0, (size_t)d_ffn * d * es, stream) != cudaSuccess)
+      return check_last("cudaMemsetAsync");
+    return kOk;
+  }
+  const int64_t ld = ffn_ld(d_ffn);
+  const int64_t dense_bytes = round_up_i64(tokens * ld * (int64_t)es, 256);
+  void* buf_z = static_cast<uint8_t*>(workspace) + kStatusBytes;
+  void* buf_u = static_cast<uint8_t*>(buf_z) + dense_bytes;   // dZ, then dU
+  void* buf_g = static_cast<uint8_t*>(buf_u) + dense_bytes;   // dG
+  GemmProblem z = problem(dtype, status, tokens, d_ffn, d);
+  z.a[0] = operand(grad_y, d, 0);
+  z.b[0] = operand(w_down_t, d, 0);
+  z.epi = store_epi(buf_u, ld, 0);
+  if ((rc = launch_gemm(z, stream)) != kOk) return rc;
+  // (padding columns [d_ffn, ld) of the dense matrices hold unspecified values; no GEMM reads them)
+  if ((rc = launch_dense_bwd(dtype, g, u, buf_u, buf_z, buf_g, tokens * ld, stream)) != kOk) return rc;
+  GemmProblem w = problem(dtype, status, d_ffn, d, tokens);
+  w.groups = 3;
+  w.a[0] = operand(buf_z, ld, 1);
+  w.b[0] = operand(grad_y, d, 1);
+  w.a[1] = operand(buf_g, ld, 1);
+  w.b[1] = operand(x, d, 1);
+  w.a[2] = operand(buf_u, ld, 1);
+  w.b[2] = operand(x, d, 1);
+  w.epi = EpiArgs{};
+  w.epi.kind = kEpiStore;
+  w.epi.c[0] = grad_w_down;
+  w.epi.ldc[0] = d_ffn;
+  w.epi.transposed[0] = 1;
+  w.epi.c[1] = grad_w_gate;
+  w.epi.ldc[1] = d;
+  w.epi.c[2] = grad_w_up;
+  w.epi.ldc[2] = d;
+  if ((rc = launch_gemm(w, stream)) != kOk) return rc;
+  GemmProblem gx = problem(dtype, status, tokens, d, d_ffn);
+  gx.k1 = (int)d_ffn;
+  gx.a[0] = operand(buf_g, ld, 0);
+  gx.b[0] = operand(w_gate, d, 1);
+  gx.a[1] = operand(buf_u, ld, 0);
+  gx.b[1] = operand(w_up, d, 1);
+  gx.epi = store_epi(grad_x, d, 0);
+  rc = launch_gemm(gx, stream);
+  prof_mark(kProfEnd, stream);
+  return rc;
+}
+
+int64_t moc_decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn) {
+  return decode_workspace_bytes(batch, d, d_ffn);
+}
+
+int moc_decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, const void* x, const void* w_gate,
+                      const void* w_up, const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes,
+                      void* stream) {
+  if (!x || !w_gate || !w_up || !w_down_t || !y) {
+    set_error("moc_decode_global: null pointer");
+    return kErrInvalidArg;
+  }
+  return decode_global(batch, d, d_ffn, k, 0, x, nullptr, w_gate, w_up, w_down_t, y, workspace, workspace_bytes,
+                       as_stream(stream));
+}
+
+int moc_decode_after_gate(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, const void* x, const void* gate_scores,
+                          const void* w_up, const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes,
+                          void* stream) {
+  if (!x || !gate_scores || !w_up || !w_down_t || !y) {
+    set_error("moc_decode_after_gate: null pointer");
+    return kErrInvalidArg;
+  }
+  return decode_global(batch, d, d_ffn, k, 0, x, gate_scores, nullptr, w_up, w_down_t, y, workspace, workspace_bytes,
+                       as_stream(stream));
+}
+
+int moc_decode_2of8(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
+                    const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !w_gate || !w_up || !w_down_t || !y) {
+    set_error("moc_decode_2of8: null pointer");
+    return kErrInvalidArg;
+  }
+  return decode_global(batch, d, d_ffn, moc_select_2of8_k(d_ffn), 1, x, nullptr, w_gate, w_up, w_down_t, y, workspace,
+                       workspace_bytes, as_stream(stream));
+}
+
+int moc_decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
+                     const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (!x || !w_gate || !w_up || !w_down_t || !y) {
+    set_error("moc_decode_dense: null pointer");
+    return kErrInvalidArg;
+  }
+  return decode_dense(batch, d, d_ffn, x, w_gate, w_up, w_down_t, y, workspace, workspace_bytes, as_stream(stream));
+}
+
+int moc_decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* sparse_z,
+                             const int16_t* idx, const void* w_down_t, void* y, void* workspace,
+                             int64_t workspace_bytes, void* stream) {
+  if (!sparse_z || !idx || !w_down_t || !y) {
+    set_error("moc_decode_selected_down: null pointer");
+    return kErrInvalidArg;
+  }
+  return decode_selected_down(batch, k, d, d_ffn, sparse_z, idx, w_down_t, y, workspace, workspace_bytes,
+                              as_stream(stream));
+}
+
 int moc_profile_begin(void** events, int capacity) {
   if (!events || capacity <= 0) {
     set_error("moc_profile_begin: need a host array of cudaEvent_t handles");

@@ -1,0 +1,436 @@
+// Decode-time MoC FFN kernels (bf16, batches of a few token rows): bandwidth-bound streaming and
+// gathering of weight rows with 128-bit coalesced loads and fp32 accumulation.
+//
+//   decode_gemv_kernel     : out[b, f] = x[b, :] . W[f, :] for every row f of W (the gate projection,
+//                            nn.Linear in moc/inference/inference_ffn.py:188, or gate and up
+//                            together for the dense baseline, inference_ffn.py:164-167)
+//   decode_sel_up_kernel   : z[b, k] = SiLU(g[b, k]) * (x[b, :] . W_up[idx[b, k], :]) - one warp per selected
+//                            channel (selected_up_silu_*_kernel,
+//                            moc/inference/cuda/optimized_global_moc_ext.cu:127-245)
+//   decode_z_from_u_kernel : same from a dense U row, used when the batch selects more rows than W_up has
+//   decode_down_kernel     : partial[s, b, :] = sum over a slice of k of z[b, k] * W_down^T[idx[b, k], :]
+//                            (selected_down_*_tile_kernel, optimized_global_moc_ext.cu:247-372; split-K as
+//                            in moc/inference/triton_fused_ffn_kernels.py:315-370 but without atomics)
+//   decode_reduce_kernel   : y[b, :] = round(sum over s of partial[s, b, :]), fixed summation order
+//
+// Rounding points follow the dense masking reference (inference_ffn.py:169-180) with bf16 tensors:
+// gate scores, U, s = SiLU(g), z = s * u and y are each rounded to bf16 once.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace moc {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
+  const uint32_t a[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(a[j] << 16);
+    v[2 * j + 1] = __uint_as_float(a[j] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+__device__ __forceinline__ float bf16_round(float v) { return Num<bf16>::round(v); }
+__device__ __forceinline__ float bf16_load(const bf16* p) { return __bfloat162float(*p); }
+
+constexpr int kGemvWarps = 8;
+constexpr int kGemvRowsPerWarp = 2;
+constexpr int kGemvRowsPerCta = kGemvWarps * kGemvRowsPerWarp;
+
+// BT batch rows of x (a tile of the batch) stay in shared memory; every warp streams two weight rows
+// at a time and reuses each x vector for both. FUSED: rows of W_gate and W_up are streamed together and
+// out = round(round(SiLU(round(g))) * round(u)) (dense SwiGLU); otherwise out = round(x . W[f]).
+template <int BT, bool FUSED>
+__global__ void __launch_bounds__(kGemvWarps * 32)
+decode_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ w2,
+                   bf16* __restrict__ out, int64_t ld_out, int batch, int d, int rows) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  uint4* xs = reinterpret_cast<uint4*>(gemv_smem);   // [BT][d / 8]
+  const int nvec = d >> 3;
+  const int b0 = blockIdx.y * BT;
+  for (int i = threadIdx.x; i < BT * nvec; i += blockDim.x) {
+    const int b = i / nvec, v = i - b * nvec;
+    xs[i] = (b0 + b < batch) ? reinterpret_cast<const uint4*>(x + static_cast<int64_t>(b0 + b) * d)[v]
+                             : make_uint4(0u, 0u, 0u, 0u);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * kGemvRowsPerCta + warp * kGemvRowsPerWarp;
+  if (f0 >= rows) return;
+  const int f1 = min(f0 + 1, rows - 1);   // a clamped duplicate row when the count is odd
+  const uint4* wr0 = reinterpret_cast<const uint4*>(w + static_cast<int64_t>(f0) * d);
+  const uint4* wr1 = reinterpret_cast<const uint4*>(w + static_cast<int64_t>(f1) * d);
+  const uint4* ur0 = FUSED ? reinterpret_cast<const uint4*>(w2 + static_cast<int64_t>(f0) * d) : nullptr;
+  const uint4* ur1 = FUSED ? reinterpret_cast<const uint4*>(w2 + static_cast<int64_t>(f1) * d) : nullptr;
+  float acc0[BT], acc1[BT], uac0[FUSED ? BT : 1], uac1[FUSED ? BT : 1];
+#pragma unroll
+  for (int b = 0; b < BT; ++b) {
+    acc0[b] = 0.0f;
+    acc1[b] = 0.0f;
+    if (FUSED) {
+      uac0[b] = 0.0f;
+      uac1[b] = 0.0f;
+    }
+  }
+#pragma unroll 2
+  for (int v = lane; v < nvec; v += 32) {
+    float a0[8], a1[8], c0[8], c1[8];
+    unpack8(wr0[v], a0);
+    unpack8(wr1[v], a1);
+    if (FUSED) {
+      unpack8(ur0[v], c0);
+      unpack8(ur1[v], c1);
+    }
+#pragma unroll
+    for (int b = 0; b < BT; ++b) {
+      float xv[8];
+      unpack8(xs[b * nvec + v], xv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc0[b] = fmaf(xv[j], a0[j], acc0[b]);
+        acc1[b] = fmaf(xv[j], a1[j], acc1[b]);
+        if (FUSED) {
+          uac0[b] = fmaf(xv[j], c0[j], uac0[b]);
+          uac1[b] = fmaf(xv[j], c1[j], uac1[b]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < BT; ++b) {
+    float r0 = warp_sum(acc0[b]), r1 = warp_sum(acc1[b]);
+    if (FUSED) {
+      const float u0 = bf16_round(warp_sum(uac0[b])), u1 = bf16_round(warp_sum(uac1[b]));
+      r0 = silu_round<bf16>(bf16_round(r0)) * u0;
+      r1 = silu_round<bf16>(bf16_round(r1)) * u1;
+    }
+    if (lane == 0 && b0 + b < batch) {
+      bf16* o = out + static_cast<int64_t>(b0 + b) * ld_out;
+      o[f0] = __float2bfloat16_rn(r0);
+      if (f0 + 1 < rows) o[f0 + 1] = __float2bfloat16_rn(r1);
+    }
+  }
+}
+
+// One warp per (b, k): z = round(round(SiLU(g)) * round(x[b] . W_up[idx[b, k]])).
+__global__ void __launch_bounds__(256)
+decode_sel_up_kernel(const bf16* __restrict__ x, const bf16* __restrict__ g_sel, const int16_t* __restrict__ idx,
+                     const bf16* __restrict__ w_up, bf16* __restrict__ z, int batch, int d, int k) {
+  const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<int64_t>(batch) * k) return;
+  const int b = static_cast<int>(wid / k);
+  const int row = idx[wid];
+  const uint4* wr = reinterpret_cast<const uint4*>(w_up + static_cast<int64_t>(row) * d);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(b) * d);
+  const int nvec = d >> 3;
+  float acc = 0.0f;
+#pragma unroll 4
+  for (int v = lane; v < nvec; v += 32) {
+    float a[8], xv[8];
+    unpack8(wr[v], a);
+    unpack8(xr[v], xv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc = fmaf(xv[j], a[j], acc);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const float s = silu_round<bf16>(bf16_load(g_sel + wid));
+    z[wid] = __float2bfloat16_rn(s * bf16_round(acc));
+  }
+}
+
+// z[b, k] = round(round(SiLU(g[b, k])) * U[b, idx[b, k]]) from a dense (already rounded) U.
+__global__ void decode_z_from_u_kernel(const bf16* __restrict__ u, int64_t ld_u, const bf16* __restrict__ g_sel,
+                                       const int16_t* __restrict__ idx, bf16* __restrict__ z, int batch, int k) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<int64_t>(batch) * k) return;
+  const int b = static_cast<int>(i / k);
+  const float s = silu_round<bf16>(bf16_load(g_sel + i));
+  z[i] = __float2bfloat16_rn(s * bf16_load(u + static_cast<int64_t>(b) * ld_u + idx[i]));
+}
+
+constexpr int kDownMaxRows = 256;
+
+// grid = (splits, d / (THREADS * 8), batch). Each thread owns 8 output columns and walks the rows of
+// its k-slice with independent 16-byte loads (unrolled: many loads in flight per thread).
+// idx == null: rows are k0, k0 + 1, ... (dense down projection through W_down^T).
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+decode_down_kernel(const bf16* __restrict__ z, const int16_t* __restrict__ idx, const bf16* __restrict__ w_down_t,
+                   float* __restrict__ partial, int batch, int k, int d, int rows_per_split) {
+  __shared__ int rows[kDownMaxRows];
+  __shared__ float zs[kDownMaxRows];
+  const int b = blockIdx.z, s = blockIdx.x;
+  const int k0 = s * rows_per_split;
+  const int n = min(rows_per_split, k - k0);
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    rows[i] = idx ? static_cast<int>(idx[static_cast<int64_t>(b) * k + k0 + i]) : k0 + i;
+    zs[i] = bf16_load(z + static_cast<int64_t>(b) * k + k0 + i);
+  }
+  __syncthreads();
+  const int col = (blockIdx.y * THREADS + threadIdx.x) * 8;
+  if (col >= d) return;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 8
+  for (int i = 0; i < n; ++i) {
+    const uint4 q = *reinterpret_cast<const uint4*>(w_down_t + static_cast<int64_t>(rows[i]) * d + col);
+    float wv[8];
+    unpack8(q, wv);
+    const float zv = zs[i];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = fmaf(zv, wv[j], acc[j]);
+  }
+  float4* out = reinterpret_cast<float4*>(partial + (static_cast<int64_t>(s) * batch + b) * d + col);
+  out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+// y[b, c..c+4) = round(sum_s partial[s, b, c..c+4)), summed in split order.
+__global__ void decode_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ y, int batch, int d,
+                                     int splits) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t n4 = static_cast<int64_t>(batch) * d / 4;
+  if (i >= n4) return;
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int s = 0; s < splits; ++s) {
+    const float4 p = reinterpret_cast<const float4*>(partial)[static_cast<int64_t>(s) * n4 + i];
+    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+  }
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&lo);
+  o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  reinterpret_cast<uint2*>(y)[i] = o;
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+struct DownPlan {
+  int threads;          // 128 or 256
+  int dchunks;
+  int rows_per_split;
+  int splits;
+};
+
+static int device_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+static DownPlan plan_down(int batch, int d, int k) {
+  DownPlan p;
+  p.threads = (batch <= 2 && d <= 4096) ? 128 : 256;
+  p.dchunks = ceil_div_i(d, p.threads * 8);
+  const int target = device_sms() * 3 / 2;
+  int splits = ceil_div_i(target, batch * p.dchunks);
+  if (splits < 1) splits = 1;
+  int rps = ceil_div_i(k, splits);
+  if (rps < 8) rps = 8;
+  if (rps > kDownMaxRows) rps = kDownMaxRows;
+  p.rows_per_split = rps;
+  p.splits = ceil_div_i(k, rps);
+  return p;
+}
+
+struct DecodeWs {
+  int* status;
+  bf16* gate;        // [batch, ld]
+  bf16* u;           // [batch, ld]
+  int16_t* idx;      // [batch, d_ffn]
+  bf16* g_sel;       // [batch, d_ffn]
+  bf16* z;           // [batch, d_ffn]
+  uint32_t* bitmap;  // [batch, words]
+  uint16_t* rank0;   // [batch, words]
+  float* partial;    // [splits, batch, d]
+  int64_t bytes;
+};
+
+static int64_t partial_bound(int64_t batch, int64_t d, int64_t d_ffn) {
+  // plan_down: splits <= target / (batch * dchunks) + 2, or ceil(k / kDownMaxRows) when the slice cap binds
+  const int64_t by_target = static_cast<int64_t>(device_sms()) * 3 / 2 + 2 * batch + 8;
+  const int64_t by_cap = batch * ((d_ffn + kDownMaxRows - 1) / kDownMaxRows + 1);
+  return (by_target > by_cap ? by_target : by_cap) * d * 4;
+}
+
+static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
+  DecodeWs w;
+  const int64_t ld = ffn_ld(d_ffn), words = mask_words(d_ffn);
+  uint8_t* p = static_cast<uint8_t*>(base);
+  auto take = [&](int64_t nbytes) {
+    uint8_t* r = p;
+    p += round_up_i64(nbytes, 256);
+    return r;
+  };
+  w.status = reinterpret_cast<int*>(take(256));
+  w.gate = reinterpret_cast<bf16*>(take(batch * ld * 2));
+  w.u = reinterpret_cast<bf16*>(take(batch * ld * 2));
+  w.idx = reinterpret_cast<int16_t*>(take(batch * d_ffn * 2));
+  w.g_sel = reinterpret_cast<bf16*>(take(batch * d_ffn * 2));
+  w.z = reinterpret_cast<bf16*>(take(batch * d_ffn * 2));
+  w.bitmap = reinterpret_cast<uint32_t*>(take(batch * words * 4));
+  w.rank0 = reinterpret_cast<uint16_t*>(take(batch * words * 2));
+  w.partial = reinterpret_cast<float*>(take(partial_bound(batch, d, d_ffn)));
+  w.bytes = p - static_cast<uint8_t*>(base);
+  return w;
+}
+
+int64_t decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn) {
+  return carve(nullptr, batch, d, d_ffn).bytes;
+}
+
+template <bool FUSED>
+static int launch_gemv(const bf16* x, const bf16* w, const bf16* w2, bf16* out, int64_t ld_out, int batch, int d,
+                       int rows, cudaStream_t stream) {
+  const int bt = batch >= 8 ? 8 : (batch >= 4 ? 4 : (batch >= 2 ? 2 : 1));
+  const dim3 grid(ceil_div_i(rows, kGemvRowsPerCta), ceil_div_i(batch, bt));
+  const size_t smem = static_cast<size_t>(bt) * d * 2;
+  prof_mark(kProfDecodeGate, stream);
+#define MOC_GEMV(BT)                                                                                              \
+  do {                                                                                                            \
+    auto kern = decode_gemv_kernel<BT, FUSED>;                                                                    \
+    if (smem > 48 * 1024 &&                                                                                       \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=        \
+            cudaSuccess)                                                                                          \
+      return check_last("decode_gemv smem attribute");                                                            \
+    kern<<<grid, kGemvWarps * 32, smem, stream>>>(x, w, w2, out, ld_out, batch, d, rows);                         \
+  } while (0)
+  if (bt == 8) MOC_GEMV(8);
+  else if (bt == 4) MOC_GEMV(4);
+  else if (bt == 2) MOC_GEMV(2);
+  else MOC_GEMV(1);
+#undef MOC_GEMV
+  return check_last("decode_gemv");
+}
+
+static int launch_down(const bf16* z, const int16_t* idx, const bf16* w_down_t, bf16* y, float* partial, int batch,
+                       int k, int d, cudaStream_t stream) {
+  const DownPlan p = plan_down(batch, d, k);
+  const dim3 grid(p.splits, p.dchunks, batch);
+  prof_mark(kProfDecodeDown, stream);
+  if (p.threads == 128)
+    decode_down_kernel<128><<<grid, 128, 0, stream>>>(z, idx, w_down_t, partial, batch, k, d, p.rows_per_split);
+  else
+    decode_down_kernel<256><<<grid, 256, 0, stream>>>(z, idx, w_down_t, partial, batch, k, d, p.rows_per_split);
+  int rc = check_last("decode_down");
+  if (rc != kOk) return rc;
+  const int64_t n4 = static_cast<int64_t>(batch) * d / 4;
+  decode_reduce_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(partial, y, batch, d, p.splits);
+  return check_last("decode_reduce");
+}
+
+// after the channel set is known: z for the selected channels, then the gathered down projection
+static int selected_tail(const DecodeWs& w, const bf16* x, const bf16* w_up, const bf16* w_down_t, bf16* y, int batch,
+                         int d, int d_ffn, int k, cudaStream_t stream) {
+  int rc;
+  const int64_t total = static_cast<int64_t>(batch) * k;
+  if (total > d_ffn) {
+    // the batch selects more rows than W_up has: one dense pass over W_up, then pick
+    if ((rc = launch_gemv<false>(x, w_up, nullptr, w.u, ffn_ld(d_ffn), batch, d, d_ffn, stream)) != kOk) return rc;
+    prof_mark(kProfDecodeUp, stream);
+    decode_z_from_u_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(w.u, ffn_ld(d_ffn), w.g_sel,
+                                                                                         w.idx, w.z, batch, k);
+  } else {
+    prof_mark(kProfDecodeUp, stream);
+    decode_sel_up_kernel<<<static_cast<unsigned>((total * 32 + 255) / 256), 256, 0, stream>>>(x, w.g_sel, w.idx, w_up,
+                                                                                              w.z, batch, d, k);
+  }
+  if ((rc = check_last("decode_up")) != kOk) return rc;
+  return launch_down(w.z, w.idx, w_down_t, y, w.partial, batch, k, d, stream);
+}
+
+static int check_decode_args(const char* who, int64_t batch, int64_t d, int64_t d_ffn, int64_t k, const void* ws,
+                             int64_t ws_bytes) {
+  if (batch < 0 || d <= 0 || d_ffn <= 0 || k <= 0 || k > d_ffn) {
+    set_error("%s: bad sizes batch=%lld d=%lld d_ffn=%lld k=%lld", who, (long long)batch, (long long)d,
+              (long long)d_ffn, (long long)k);
+    return kErrInvalidArg;
+  }
+  if (d % 8 != 0 || d_ffn > 32768 || batch > 65535) {
+    set_error("%s: needs d %% 8 == 0, d_ffn <= 32768 and batch <= 65535", who);
+    return kErrUnsupported;
+  }
+  if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0 || ws_bytes < decode_workspace_bytes(batch, d, d_ffn)) {
+    set_error("%s: workspace missing, not 256-byte aligned or smaller than %lld bytes", who,
+              (long long)decode_workspace_bytes(batch, d, d_ffn));
+    return kErrWorkspace;
+  }
+  return kOk;
+}
+
+int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, const void* x, const void* gate_scores,
+                  const void* w_gate, const void* w_up, const void* w_down_t, void* y, void* workspace,
+                  int64_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_decode_args("moc_decode", batch, d, d_ffn, k, workspace, workspace_bytes);
+  if (rc != kOk) return rc;
+  if (batch == 0) return kOk;
+  const DecodeWs w = carve(workspace, batch, d, d_ffn);
+  const bf16* xb = static_cast<const bf16*>(x);
+  void* scores = w.gate;
+  int64_t ld_scores = ffn_ld(d_ffn);
+  if (gate_scores) {   // scores computed by the caller: contiguous [batch, d_ffn]
+    scores = const_cast<void*>(gate_scores);
+    ld_scores = d_ffn;
+  } else if ((rc = launch_gemv<false>(xb, static_cast<const bf16*>(w_gate), nullptr, w.gate, ld_scores, (int)batch,
+                                      (int)d, (int)d_ffn, stream)) != kOk) {
+    return rc;
+  }
+  if (rule == 0)
+    rc = launch_topk_select(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, (int)k, 0, w.idx, w.g_sel, w.bitmap,
+                            w.rank0, stream);
+  else
+    rc = launch_select_2of8(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, 0, w.idx, w.g_sel, w.bitmap, w.rank0,
+                            stream);
+  if (rc != kOk) return rc;
+  rc = selected_tail(w, xb, static_cast<const bf16*>(w_up), static_cast<const bf16*>(w_down_t),
+                     static_cast<bf16*>(y), (int)batch, (int)d, (int)d_ffn, (int)k, stream);
+  prof_mark(kProfEnd, stream);
+  return rc;
+}
+
+int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
+                 const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_decode_args("moc_decode_dense", batch, d, d_ffn, d_ffn, workspace, workspace_bytes);
+  if (rc != kOk) return rc;
+  if (batch == 0) return kOk;
+  const DecodeWs w = carve(workspace, batch, d, d_ffn);
+  // z[b, f] = SiLU(g) * u for every channel, stored with row stride d_ffn so that it reads as a compact z
+  if ((rc = launch_gemv<true>(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate),
+                              static_cast<const bf16*>(w_up), w.z, d_ffn, (int)batch, (int)d, (int)d_ffn, stream)) !=
+      kOk)
+    return rc;
+  rc = launch_down(w.z, nullptr, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), w.partial, (int)batch,
+                   (int)d_ffn, (int)d, stream);
+  prof_mark(kProfEnd, stream);
+  return rc;
+}
+
+int decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* z, const int16_t* idx,
+                         const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
+  int rc = check_decode_args("moc_decode_selected_down", batch, d, d_ffn, k, workspace, workspace_bytes);
+  if (rc != kOk) return rc;
+  if (batch == 0) return kOk;
+  const DecodeWs w = carve(workspace, batch, d, d_ffn);
+  return launch_down(static_cast<const bf16*>(z), idx, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y),
+                     w.partial, (int)batch, (int)k, (int)d, stream);
+}
+
+}  // namespace moc

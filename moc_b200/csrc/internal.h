@@ -64,6 +64,9 @@ int launch_gather_sel(int dtype, const int16_t* idx, const void* u_dense, const 
 // dZ[tokens, ld] (in) -> dG' (grad_g_out) and dU' (written over dZ in place): gather, SiLU', zero fill
 int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
                       void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
+// dense SwiGLU backward, elementwise over tokens * ld elements (a multiple of 128)
+int launch_dense_bwd(int dtype, const void* g, const void* u, void* dz_to_du, void* z_out, void* grad_g_out,
+                     int64_t elems, cudaStream_t stream);
 // out[cols, rows] <- in[rows, cols]^T
 int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_t ld_out, int rows, int cols,
                      cudaStream_t stream);
@@ -78,6 +81,17 @@ enum ProfTag : int {
   kProfDecodeDense = 11, kProfBwdSparse = 12, kProfGatherSel = 13,
 };
 void prof_mark(int tag, cudaStream_t stream);
+
+// ---- decode path (decode.cu), bf16 only ---------------------------------------------------------
+int64_t decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn);
+// rule 0: global Top-K, 1: 2-of-8. gate_scores != null: use the caller's [batch, d_ffn] scores instead of x * W_gate^T
+int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, const void* x, const void* gate_scores,
+                  const void* w_gate, const void* w_up, const void* w_down_t, void* y, void* workspace,
+                  int64_t workspace_bytes, cudaStream_t stream);
+int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
+                 const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, cudaStream_t stream);
+int decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* z, const int16_t* idx,
+                         const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, cudaStream_t stream);
 
 int check_last(const char* what);
 const char* last_error_text();

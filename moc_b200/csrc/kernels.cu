@@ -523,6 +523,36 @@ bwd_sparse_kernel(const int16_t* __restrict__ idx, const T* __restrict__ g_sel, 
   row_store(urow, dzrow, static_cast<int>(ld));
 }
 
+// Dense SwiGLU backward, elementwise part (autograd of moc/ffn.py:120-121 with stored-dtype tensors):
+// s = round(SiLU(g)), z = round(s * u); grad_u = round(dz * s), grad_s = round(dz * u),
+// grad_g = round(grad_s * SiLU'(g)) with SiLU' evaluated in fp32 in one step (PyTorch's silu_backward).
+// dz is overwritten by grad_u in place; z and grad_g go to their own buffers. One thread per 16 bytes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dense_bwd_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ dz_du, T* __restrict__ z_out,
+                 T* __restrict__ grad_g, int64_t nvec) {
+  constexpr int E = 16 / sizeof(T);
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  __align__(16) T gv[E], uv[E], dv[E], zo[E], go[E], uo[E];
+  *reinterpret_cast<uint4*>(gv) = reinterpret_cast<const uint4*>(g)[i];
+  *reinterpret_cast<uint4*>(uv) = reinterpret_cast<const uint4*>(u)[i];
+  *reinterpret_cast<uint4*>(dv) = reinterpret_cast<const uint4*>(dz_du)[i];
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const float gf = Num<T>::to_float(gv[j]), uf = Num<T>::to_float(uv[j]), dz = Num<T>::to_float(dv[j]);
+    const float sig = sigmoid_act<T>(gf);
+    const float s = Num<T>::round(gf * sig);
+    zo[j] = Num<T>::from_float(s * uf);
+    uo[j] = Num<T>::from_float(dz * s);
+    const float gs = Num<T>::round(dz * uf);
+    go[j] = Num<T>::from_float(gs * (sig * (1.0f + gf * (1.0f - sig))));
+  }
+  reinterpret_cast<uint4*>(z_out)[i] = *reinterpret_cast<const uint4*>(zo);
+  reinterpret_cast<uint4*>(grad_g)[i] = *reinterpret_cast<const uint4*>(go);
+  reinterpret_cast<uint4*>(dz_du)[i] = *reinterpret_cast<const uint4*>(uo);
+}
+
 template <typename T>
 __global__ void transpose_kernel(const T* __restrict__ in, int64_t ld_in, T* __restrict__ out, int64_t ld_out,
                                  int rows, int cols) {
@@ -679,6 +709,25 @@ int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const vo
                                                                 static_cast<T*>(grad_g_out), ld, k);
   }
   return check_last("bwd_sparse");
+}
+
+int launch_dense_bwd(int dtype, const void* g, const void* u, void* dz_to_du, void* z_out, void* grad_g_out,
+                     int64_t elems, cudaStream_t stream) {
+  if (elems == 0) return kOk;
+  prof_mark(kProfBwdSparse, stream);
+  if (dtype == kBF16) {
+    const int64_t nvec = elems / 8;
+    dense_bwd_kernel<__nv_bfloat16><<<static_cast<unsigned>((nvec + 255) / 256), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(u),
+        static_cast<__nv_bfloat16*>(dz_to_du), static_cast<__nv_bfloat16*>(z_out),
+        static_cast<__nv_bfloat16*>(grad_g_out), nvec);
+  } else {
+    const int64_t nvec = elems / 4;
+    dense_bwd_kernel<float><<<static_cast<unsigned>((nvec + 255) / 256), 256, 0, stream>>>(
+        static_cast<const float*>(g), static_cast<const float*>(u), static_cast<float*>(dz_to_du),
+        static_cast<float*>(z_out), static_cast<float*>(grad_g_out), nvec);
+  }
+  return check_last("dense_bwd");
 }
 
 int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_t ld_out, int rows, int cols,

@@ -211,3 +211,46 @@ def test_full_size_properties():
     hi_unsel = torch.where(sel, torch.full_like(g.float(), float("-inf")), g.float()).max(dim=1).values
     # gates from two GEMM implementations can each be off by one bf16 ulp, in opposite directions
     assert (lo_sel >= hi_unsel - 2 ** -6 * hi_unsel.abs()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,d,d_ffn", [(24, 64, 173), (129, 256, 1000), (300, 512, 1376)])
+def test_dense_ffn_matches_autograd_reference(dtype, tokens, d, d_ffn):
+    """ffn_type="dense" (StandardSwiGLUFFN, moc/ffn.py:111-121) on the B200 GEMM core against PyTorch autograd
+    on the CPU."""
+    x, grad_y, wg, wu, wd = O.make_inputs(tokens, d, d_ffn, dtype, seed=tokens)
+    m = build_ffn(d, d_ffn, "dense").to(device="cuda", dtype=dtype)
+    with torch.no_grad():
+        m.gate_proj.weight.copy_(wg)
+        m.up_proj.weight.copy_(wu)
+        m.down_proj.weight.copy_(wd)
+    xs = x.cuda().requires_grad_(True)
+    moc_b200.set_status_checks(True)
+    try:
+        y = m(xs)
+        y.backward(grad_y.cuda())
+    finally:
+        moc_b200.set_status_checks(False)
+    ref = O.dense_forward_backward(x, wg, wu, wd, grad_y)
+    got = dict(y=y.detach().cpu(), dx=xs.grad.cpu(), d_gate_w=m.gate_proj.weight.grad.cpu(),
+               d_up_w=m.up_proj.weight.grad.cpu(), d_down_w=m.down_proj.weight.grad.cpu())
+    _compare(got, dict(zip(("y", "dx", "d_gate_w", "d_up_w", "d_down_w"), ref)), dtype, f"dense[{tokens},{d},{d_ffn}]")
+
+
+def test_materialized_saved_set_matches_oracle():
+    """moc_ffn_fwd can also write the reference's full saved set (s_sel, z_sel, moc/ffn.py:166-169)."""
+    tokens, d, d_ffn, k = 65, 128, 300, 50
+    x, grad_y, wg, wu, wd = O.make_inputs(tokens, d, d_ffn, torch.bfloat16, seed=9)
+    m = _module("moc", d, d_ffn, k, torch.bfloat16, wg, wu, wd)
+    m.materialize_sz = True
+    from moc_b200.ffn import moc_ffn_forward, transpose_weight
+    y, idx, g_sel, u_sel, s_sel, z_sel, bitmap, rank0 = moc_ffn_forward(
+        x.cuda(), wg.cuda(), wu.cuda(), transpose_weight(wd.cuda()), k, _lib.SELECT_TOPK, save_sz=True)
+    ref = O.moc_forward(x, wg, wu, wd, k, idx_override=idx.cpu().to(torch.int64))
+    assert torch.equal(g_sel.cpu(), ref["g_sel"]) or rel_l2(g_sel.cpu(), ref["g_sel"]) < 1e-2
+    for got, key in ((u_sel, "u_sel"), (s_sel, "s_sel"), (z_sel, "z_sel"), (y, "y")):
+        assert rel_l2(got.cpu(), ref[key]) < 1e-2, key
+    xs = x.cuda().requires_grad_(True)
+    out = m(xs)
+    out.backward(grad_y.cuda())
+    assert torch.isfinite(xs.grad.float()).all()
