@@ -177,6 +177,26 @@ int moc_decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn,
                              const int16_t* idx, const void* w_down_t, void* y, void* workspace,
                              int64_t workspace_bytes, void* stream);
 
+/* Global MoC decode FFN without any caller-provided scratch: same computation and same result as
+ * moc_decode_global, for callers that must not allocate device memory when they call (a fixed memory
+ * budget that is already handed out, a frozen allocator in a serving loop, a runtime that passes a
+ * plugin nothing but its inputs and outputs). The scratch is a fixed 6 MiB array inside the library's
+ * device image, present on every GPU that loads the library for the life of the process. No counterpart
+ * in the reference (its decode ops allocate their outputs and temporaries with torch::empty,
+ * moc/inference/cuda/optimized_global_moc_ext.cu:468-472).
+ *   Limits: batch <= moc_decode_static_max_batch() (8), d <= moc_decode_static_max_d() (4096),
+ *   d_ffn <= moc_decode_static_max_d_ffn() (8192); larger sizes return MOC_ERR_UNSUPPORTED.
+ *   The first call on each device looks up the scratch address (the device must be current); make that
+ *   first call outside any stream capture. The call itself allocates nothing.
+ *   All calls on a device share the one scratch array: calls that may overlap on the GPU (different
+ *   streams, or several host threads) race with each other; serialise them. Nothing in the scratch
+ *   needs clearing between calls: every part is rewritten before it is read. */
+int moc_decode_global_static(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, const void* x, const void* w_gate,
+                             const void* w_up, const void* w_down_t, void* y, void* stream);
+int64_t moc_decode_static_max_batch(void);
+int64_t moc_decode_static_max_d(void);
+int64_t moc_decode_static_max_d_ffn(void);
+
 /* Per-kernel timing without a profiler. Between moc_profile_begin and moc_profile_end (process-wide,
  * one profile at a time) the library records events[0], events[1], ... (a HOST array of created
  * cudaEvent_t handles, timing enabled) on the stream of each call, one right before every

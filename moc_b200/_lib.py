@@ -46,6 +46,10 @@ SIGNATURES = {
     "moc_decode_after_gate": (c_int, [c_int64] * 4 + [_P] * 6 + [c_int64, _P]),
     "moc_decode_2of8": (c_int, [c_int64] * 3 + [_P] * 6 + [c_int64, _P]),
     "moc_decode_dense": (c_int, [c_int64] * 3 + [_P] * 6 + [c_int64, _P]),
+    "moc_decode_global_static": (c_int, [c_int64] * 4 + [_P] * 5 + [_P]),
+    "moc_decode_static_max_batch": (c_int64, []),
+    "moc_decode_static_max_d": (c_int64, []),
+    "moc_decode_static_max_d_ffn": (c_int64, []),
     "moc_decode_selected_down": (c_int, [c_int64] * 4 + [_P] * 5 + [c_int64, _P]),
 }
 
