@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode FFN micro-benchmark (N=1 only)")
     return ap.parse_args()
 
 
@@ -205,6 +206,76 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+def bench_decode(dev, peaks, layers=24, groups=20):
+    """Decode FFN latency at the 1b shape (BASELINE config 3): batches of 1, 8, 64 rows, global MoC (K=1024),
+    MoC 2:8 and dense. One CUDA graph holds `layers` FFN calls, each on its own weight set (24 x 89 MB, far
+    beyond the 126 MB L2, so weights stream from HBM as in a 24-layer decode step); the graph is replayed
+    `groups` times between two CUDA events. Reports microseconds per FFN call and per token, and the
+    achieved HBM bandwidth on the algorithmic bytes of the call."""
+    import torch
+
+    from moc_b200.inference import InferenceMoCSwiGLUFFN
+
+    k2 = (D_FFN // 8) * 2 + min(2, D_FFN % 8)
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def make(k, grouped):
+        mods = []
+        for _ in range(layers):
+            m = InferenceMoCSwiGLUFFN(D, D_FFN, k, *((2, 8) if grouped else (None, None)))
+            m = m.to(device=dev, dtype=torch.bfloat16)
+            with torch.no_grad():
+                for p in m.parameters():
+                    p.copy_(torch.randn(p.shape, device=dev, generator=gen) * 0.02)
+            m.freeze_for_compile()
+            mods.append(m)
+        return mods
+
+    results = {}
+    mods_global = make(K_SEL, False)
+    mods_28 = make(k2, True)
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    for mode, mods, label in (("auto", mods_global, "global_moc"), ("auto", mods_28, "moc_2of8"),
+                              ("dense_baseline", mods_global, "dense")):
+        for batch in (1, 8, 64):
+            x = torch.randn(batch, D, device=dev, dtype=torch.bfloat16, generator=gen)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for m in mods:
+                    m(x, mode=mode)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for m in mods:
+                    m(x, mode=mode)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(groups):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us_call = 1e3 * e0.elapsed_time(e1) / (groups * layers)
+            ksel = K_SEL if label == "global_moc" else k2
+            if label == "dense":
+                nbytes = 3 * D_FFN * D * 2
+            else:   # gate fully streamed; up rows gathered (or W_up streamed once when batch * k > d_ffn); down rows gathered
+                up_rows = min(batch * ksel, D_FFN)
+                nbytes = D_FFN * D * 2 + up_rows * D * 2 + min(batch * ksel, D_FFN) * D * 2
+            results[f"{label}_b{batch}"] = {
+                "us_per_call": us_call, "us_per_token": us_call / batch,
+                "algorithmic_mb": nbytes / 1e6, "achieved_gbs": nbytes / (us_call * 1e-6) / 1e9,
+                "hbm_frac": nbytes / (us_call * 1e-6) / 1e9 / hbm,
+            }
+            del graph
+    results["protocol"] = (f"{layers} distinct weight sets per CUDA graph (HBM-resident, not L2), {groups} replays, "
+                           "CUDA events; down/up bytes count distinct-row upper bounds")
+    return results
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -332,27 +403,55 @@ def run_ours(args, rank, world, local_rank):
     # ---- e2e: host (pinned) inputs in, host outputs back, every step ----
     e2e = None
     if not args.no_e2e:
-        y_host = torch.empty_like(x_host)
-        dx_host = torch.empty_like(x_host)
-        x_dev = torch.empty_like(x).requires_grad_(True)
-        dy_dev = torch.empty_like(dy)
+        # Software pipeline over steps, as an input pipeline would run it: the host->device copy of step i+1
+        # and the device->host copy of step i-1 overlap the kernels of step i (two device buffer sets, one
+        # copy stream per direction). Every copy of every step is inside the timed region.
+        y_host = [torch.empty_like(x_host) for _ in range(2)]
+        dx_host = [torch.empty_like(x_host) for _ in range(2)]
+        x_dev = [torch.empty_like(x).requires_grad_(True) for _ in range(2)]
+        dy_dev = [torch.empty_like(dy) for _ in range(2)]
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        compute_done = [torch.cuda.Event() for _ in range(2)]
+        s_in, s_out, s_main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
 
-        def e2e_step():
-            with torch.no_grad():
-                x_dev.copy_(x_host, non_blocking=True)
-                dy_dev.copy_(dy_host, non_blocking=True)
-            y = step(x_dev, dy_dev)
-            y_host.copy_(y.detach(), non_blocking=True)
-            dx_host.copy_(x_dev.grad, non_blocking=True)
+        def h2d(i):
+            j = i & 1
+            with torch.cuda.stream(s_in), torch.no_grad():
+                s_in.wait_event(compute_done[j])          # the kernels that last read this buffer set are done
+                x_dev[j].copy_(x_host, non_blocking=True)
+                dy_dev[j].copy_(dy_host, non_blocking=True)
+                in_ready[j].record(s_in)
 
-        for _ in range(3):
-            e2e_step()
+        def compute_and_d2h(i):
+            j = i & 1
+            s_main.wait_event(in_ready[j])
+            y = step(x_dev[j], dy_dev[j])
+            grad = x_dev[j].grad
+            compute_done[j].record(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(compute_done[j])
+                y_host[j].copy_(y.detach(), non_blocking=True)
+                dx_host[j].copy_(grad, non_blocking=True)
+                y.record_stream(s_out)
+                grad.record_stream(s_out)
+
+        def run_pipeline(n):
+            h2d(0)
+            for i in range(n):
+                if i + 1 < n:
+                    h2d(i + 1)
+                compute_and_d2h(i)
+            s_main.wait_stream(s_out)
+
+        for ev in compute_done:
+            ev.record(s_main)
+        run_pipeline(3)
         barrier()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
-            e2e_step()
+        s_in.wait_event(e0)
+        run_pipeline(args.steps)
         e1.record()
         torch.cuda.synchronize()
         barrier()
@@ -365,12 +464,17 @@ def run_ours(args, rank, world, local_rank):
         e2e = {"value": tokens * world * args.steps / (e_ms * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": 2 * nbytes,
                "ms_per_step": e_ms / args.steps,
-               "what": "module(x).backward(dy) with x, dy copied from pinned host memory and y, dx copied back, "
-                       "each step"}
+               "what": "module(x).backward(dy) with x, dy copied from pinned host memory and y, dx copied back to "
+                       "pinned host memory every step; copies of neighbouring steps overlap the kernels "
+                       "(double-buffered, one copy stream per direction)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(args.ffn_type)
+    decode = None
+    if rank == 0 and world == 1 and not args.no_decode:
+        torch.cuda.empty_cache()
+        decode = bench_decode(dev, peaks)
 
     if rank == 0:
         value = tokens * world * args.steps / (ms_total * 1e-3)
@@ -380,7 +484,7 @@ def run_ours(args, rank, world, local_rank):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args, world), "e2e": e2e, "gpu_launches": launches,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "kernels": kernel_share,
-            "host_wall_ms_per_step": 1e3 * wall / args.steps, "k_selected": k_eff,
+            "host_wall_ms_per_step": 1e3 * wall / args.steps, "k_selected": k_eff, "decode": decode,
         }
         print(json.dumps(out), flush=True)
     if world > 1:

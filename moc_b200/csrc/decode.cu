@@ -54,15 +54,17 @@ __global__ void __launch_bounds__(kGemvWarps * 32)
 decode_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ w2,
                    bf16* __restrict__ out, int64_t ld_out, int batch, int d, int rows) {
   extern __shared__ __align__(16) uint8_t gemv_smem[];
-  uint4* xs = reinterpret_cast<uint4*>(gemv_smem);   // [BT][d / 8]
+  uint4* xs = reinterpret_cast<uint4*>(gemv_smem);   // [BT][d / 8]; unused for BT <= 2 (x read through L1)
   const int nvec = d >> 3;
   const int b0 = blockIdx.y * BT;
-  for (int i = threadIdx.x; i < BT * nvec; i += blockDim.x) {
-    const int b = i / nvec, v = i - b * nvec;
-    xs[i] = (b0 + b < batch) ? reinterpret_cast<const uint4*>(x + static_cast<int64_t>(b0 + b) * d)[v]
-                             : make_uint4(0u, 0u, 0u, 0u);
+  if (BT > 2) {
+    for (int i = threadIdx.x; i < BT * nvec; i += blockDim.x) {
+      const int b = i / nvec, v = i - b * nvec;
+      xs[i] = (b0 + b < batch) ? reinterpret_cast<const uint4*>(x + static_cast<int64_t>(b0 + b) * d)[v]
+                               : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
   }
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * kGemvRowsPerCta + warp * kGemvRowsPerWarp;
   if (f0 >= rows) return;
@@ -81,7 +83,7 @@ decode_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       uac1[b] = 0.0f;
     }
   }
-#pragma unroll 2
+#pragma unroll(BT <= 2 ? 8 : 2)
   for (int v = lane; v < nvec; v += 32) {
     float a0[8], a1[8], c0[8], c1[8];
     unpack8(wr0[v], a0);
@@ -93,7 +95,12 @@ decode_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 #pragma unroll
     for (int b = 0; b < BT; ++b) {
       float xv[8];
-      unpack8(xs[b * nvec + v], xv);
+      if (BT > 2) {
+        unpack8(xs[b * nvec + v], xv);
+      } else {   // no staging and no barrier in front of the weight stream
+        const int bb = min(b0 + b, batch - 1);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(bb) * d) + v), xv);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         acc0[b] = fmaf(xv[j], a0[j], acc0[b]);
@@ -159,6 +166,16 @@ __global__ void decode_z_from_u_kernel(const bf16* __restrict__ u, int64_t ld_u,
   z[i] = __float2bfloat16_rn(s * bf16_load(u + static_cast<int64_t>(b) * ld_u + idx[i]));
 }
 
+// z[b, f] = round(round(SiLU(g[b, f])) * u[b, f]) over dense rows (dense baseline for larger batches)
+__global__ void decode_swiglu_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, int64_t ld,
+                                     bf16* __restrict__ z, int batch, int d_ffn) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<int64_t>(batch) * d_ffn) return;
+  const int b = static_cast<int>(i / d_ffn), f = static_cast<int>(i - static_cast<int64_t>(b) * d_ffn);
+  const float s = silu_round<bf16>(bf16_load(g + b * ld + f));
+  z[i] = __float2bfloat16_rn(s * bf16_load(u + b * ld + f));
+}
+
 constexpr int kDownMaxRows = 256;
 
 // grid = (splits, d / (THREADS * 8), batch). Each thread owns 8 output columns and walks the rows of
@@ -197,22 +214,41 @@ decode_down_kernel(const bf16* __restrict__ z, const int16_t* __restrict__ idx, 
   out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
-// y[b, c..c+4) = round(sum_s partial[s, b, c..c+4)), summed in split order.
-__global__ void decode_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ y, int batch, int d,
-                                     int splits) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+// y[b, c..c+4) = round(sum_s partial[s, b, c..c+4)). 16 threads share one output vector: thread j sums the
+// splits j, j + 16, ... and the 16 sums are added in a fixed tree, so the result does not depend on timing.
+constexpr int kReduceLanes = 16;
+__global__ void __launch_bounds__(256)
+decode_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ y, int batch, int d, int splits) {
+  __shared__ float4 part[256];
   const int64_t n4 = static_cast<int64_t>(batch) * d / 4;
-  if (i >= n4) return;
+  const int j = threadIdx.x & (kReduceLanes - 1);
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * (256 / kReduceLanes) + (threadIdx.x / kReduceLanes);
   float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  for (int s = 0; s < splits; ++s) {
-    const float4 p = reinterpret_cast<const float4*>(partial)[static_cast<int64_t>(s) * n4 + i];
-    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+  if (i < n4) {
+#pragma unroll 4
+    for (int s = j; s < splits; s += kReduceLanes) {
+      const float4 p = reinterpret_cast<const float4*>(partial)[static_cast<int64_t>(s) * n4 + i];
+      acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
   }
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-  uint2 o;
-  o.x = *reinterpret_cast<const uint32_t*>(&lo);
-  o.y = *reinterpret_cast<const uint32_t*>(&hi);
-  reinterpret_cast<uint2*>(y)[i] = o;
+  part[threadIdx.x] = acc;
+  __syncthreads();
+#pragma unroll
+  for (int o = kReduceLanes / 2; o > 0; o >>= 1) {
+    if (j < o) {
+      const float4 q = part[threadIdx.x + o];
+      acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+      part[threadIdx.x] = acc;
+    }
+    __syncthreads();
+  }
+  if (j == 0 && i < n4) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&lo);
+    o.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(y)[i] = o;
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -321,6 +357,34 @@ static int launch_gemv(const bf16* x, const bf16* w, const bf16* w2, bf16* out, 
   return check_last("decode_gemv");
 }
 
+// out[b, f] = round(x[b, :] . W[f, :]) for every row of W. Batches of 16 rows and more go through the tcgen05
+// GEMM core as out^T[F, batch] = W * x^T with a transposed store (43 tiles at the 1b shape, each streaming
+// 128 weight rows once); smaller batches use the CUDA-core GEMV.
+constexpr int kDecodeGemmMinBatch = 16;
+
+static int project_rows(const bf16* x, const bf16* w, bf16* out, int64_t ld_out, int batch, int d, int rows,
+                        int* status, cudaStream_t stream) {
+  if (batch < kDecodeGemmMinBatch) return launch_gemv<false>(x, w, nullptr, out, ld_out, batch, d, rows, stream);
+  GemmProblem p = {};
+  p.dtype = kBF16;
+  p.status = status;
+  p.m = rows;
+  p.n = batch;
+  p.k0 = d;
+  p.groups = 1;
+  p.a[0].ptr = w;
+  p.a[0].ld = d;
+  p.a[0].mn_major = 0;
+  p.b[0].ptr = x;
+  p.b[0].ld = d;
+  p.b[0].mn_major = 0;
+  p.epi.kind = kEpiStore;
+  p.epi.c[0] = out;
+  p.epi.ldc[0] = ld_out;
+  p.epi.transposed[0] = 1;
+  return launch_gemm(p, stream);
+}
+
 static int launch_down(const bf16* z, const int16_t* idx, const bf16* w_down_t, bf16* y, float* partial, int batch,
                        int k, int d, cudaStream_t stream) {
   const DownPlan p = plan_down(batch, d, k);
@@ -333,7 +397,9 @@ static int launch_down(const bf16* z, const int16_t* idx, const bf16* w_down_t, 
   int rc = check_last("decode_down");
   if (rc != kOk) return rc;
   const int64_t n4 = static_cast<int64_t>(batch) * d / 4;
-  decode_reduce_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(partial, y, batch, d, p.splits);
+  const int64_t per_cta = 256 / kReduceLanes;
+  decode_reduce_kernel<<<static_cast<unsigned>((n4 + per_cta - 1) / per_cta), 256, 0, stream>>>(partial, y, batch, d,
+                                                                                            p.splits);
   return check_last("decode_reduce");
 }
 
@@ -344,7 +410,7 @@ static int selected_tail(const DecodeWs& w, const bf16* x, const bf16* w_up, con
   const int64_t total = static_cast<int64_t>(batch) * k;
   if (total > d_ffn) {
     // the batch selects more rows than W_up has: one dense pass over W_up, then pick
-    if ((rc = launch_gemv<false>(x, w_up, nullptr, w.u, ffn_ld(d_ffn), batch, d, d_ffn, stream)) != kOk) return rc;
+    if ((rc = project_rows(x, w_up, w.u, ffn_ld(d_ffn), batch, d, d_ffn, w.status, stream)) != kOk) return rc;
     prof_mark(kProfDecodeUp, stream);
     decode_z_from_u_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(w.u, ffn_ld(d_ffn), w.g_sel,
                                                                                          w.idx, w.z, batch, k);
@@ -383,14 +449,16 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
   if (rc != kOk) return rc;
   if (batch == 0) return kOk;
   const DecodeWs w = carve(workspace, batch, d, d_ffn);
+  if (batch >= kDecodeGemmMinBatch && cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess)
+    return check_last("cudaMemsetAsync");
   const bf16* xb = static_cast<const bf16*>(x);
   void* scores = w.gate;
   int64_t ld_scores = ffn_ld(d_ffn);
   if (gate_scores) {   // scores computed by the caller: contiguous [batch, d_ffn]
     scores = const_cast<void*>(gate_scores);
     ld_scores = d_ffn;
-  } else if ((rc = launch_gemv<false>(xb, static_cast<const bf16*>(w_gate), nullptr, w.gate, ld_scores, (int)batch,
-                                      (int)d, (int)d_ffn, stream)) != kOk) {
+  } else if ((rc = project_rows(xb, static_cast<const bf16*>(w_gate), w.gate, ld_scores, (int)batch, (int)d,
+                                (int)d_ffn, w.status, stream)) != kOk) {
     return rc;
   }
   if (rule == 0)
@@ -413,10 +481,23 @@ int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const v
   if (batch == 0) return kOk;
   const DecodeWs w = carve(workspace, batch, d, d_ffn);
   // z[b, f] = SiLU(g) * u for every channel, stored with row stride d_ffn so that it reads as a compact z
-  if ((rc = launch_gemv<true>(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate),
-                              static_cast<const bf16*>(w_up), w.z, d_ffn, (int)batch, (int)d, (int)d_ffn, stream)) !=
-      kOk)
+  if (batch >= kDecodeGemmMinBatch) {
+    if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
+    const int64_t ld = ffn_ld(d_ffn);
+    if ((rc = project_rows(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate), w.gate, ld, (int)batch,
+                           (int)d, (int)d_ffn, w.status, stream)) != kOk ||
+        (rc = project_rows(static_cast<const bf16*>(x), static_cast<const bf16*>(w_up), w.u, ld, (int)batch, (int)d,
+                           (int)d_ffn, w.status, stream)) != kOk)
+      return rc;
+    const int64_t total = batch * d_ffn;
+    decode_swiglu_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(w.gate, w.u, ld, w.z,
+                                                                                        (int)batch, (int)d_ffn);
+    if ((rc = check_last("decode_swiglu")) != kOk) return rc;
+  } else if ((rc = launch_gemv<true>(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate),
+                                     static_cast<const bf16*>(w_up), w.z, d_ffn, (int)batch, (int)d, (int)d_ffn,
+                                     stream)) != kOk) {
     return rc;
+  }
   rc = launch_down(w.z, nullptr, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), w.partial, (int)batch,
                    (int)d_ffn, (int)d, stream);
   prof_mark(kProfEnd, stream);

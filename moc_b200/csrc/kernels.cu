@@ -157,12 +157,152 @@ topk_select_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k,
 }
 
 // ------------------------------------------------------------------------------------------
+// One CTA per token row, for calls with few rows (decode batches, tiny training batches) where one
+// warp per row would leave the GPU idle and make the call as long as one warp's serial pass.
+// Thread t owns the contiguous channels [t * chunk, (t + 1) * chunk), so thread order is channel order.
+// ------------------------------------------------------------------------------------------
+constexpr int kCtaSelThreads = 512;
+constexpr int kCtaSelWarps = kCtaSelThreads / 32;
+constexpr int kCtaSelBins = 2048;
+
+__device__ __forceinline__ uint32_t cta_exscan(uint32_t v, uint32_t* wsum /*[kCtaSelWarps]*/, uint32_t& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t nb = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= o) inc += nb;
+  }
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  uint32_t woff = 0, tot = 0;
+#pragma unroll
+  for (int i = 0; i < kCtaSelWarps; ++i) {
+    const uint32_t s = wsum[i];
+    if (i < warp) woff += s;
+    tot += s;
+  }
+  total = tot;
+  __syncthreads();
+  return woff + inc - v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kCtaSelThreads)
+topk_select_cta_kernel(T* __restrict__ g, int64_t ldg, int d_ffn, int k, int words, int write_s,
+                       int16_t* __restrict__ idx, T* __restrict__ g_sel, uint32_t* __restrict__ bitmap,
+                       uint16_t* __restrict__ rank0) {
+  using KT = KeyTraits<T>;
+  using Bits = typename KT::Bits;
+  extern __shared__ __align__(16) uint8_t cta_sel_smem[];
+  uint32_t* hist = reinterpret_cast<uint32_t*>(cta_sel_smem);   // [kCtaSelBins]
+  uint32_t* bm = hist + kCtaSelBins;                            // [words]
+  Bits* raw = reinterpret_cast<Bits*>(bm + words);              // [d_ffn] raw bit patterns of the row
+  __shared__ uint32_t wsum[kCtaSelWarps];
+  __shared__ uint32_t found[2];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  Bits* grow = reinterpret_cast<Bits*>(g) + static_cast<int64_t>(row) * ldg;
+  for (int i = tid; i < d_ffn; i += kCtaSelThreads) raw[i] = grow[i];
+  for (int w = tid; w < words; w += kCtaSelThreads) bm[w] = 0u;
+  __syncthreads();
+
+  // ---- K-th largest key, one digit per pass ----
+  uint32_t prefix = 0, prefix_mask = 0, k_rem = static_cast<uint32_t>(k);
+  int hi_bit = KT::kBits;
+#pragma unroll 1
+  while (hi_bit > 0) {
+    const int nbits = (hi_bit == 32) ? 11 : (hi_bit >= 11 ? 11 : hi_bit);
+    const int shift = hi_bit - nbits;
+    const int nbins = 1 << nbits;
+    for (int b = tid; b < nbins; b += kCtaSelThreads) hist[b] = 0u;
+    __syncthreads();
+    for (int i = tid; i < d_ffn; i += kCtaSelThreads) {
+      const uint32_t key = KT::key(raw[i]);
+      if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & (nbins - 1)], 1u);
+    }
+    __syncthreads();
+    const int per = nbins >= kCtaSelThreads ? nbins / kCtaSelThreads : 1;
+    const int lo = (kCtaSelThreads - 1 - tid) * per;   // bins counted from the top
+    uint32_t local = 0;
+    if (lo < nbins)
+      for (int b = 0; b < per; ++b) local += hist[lo + b];
+    uint32_t total = 0;
+    uint32_t above = cta_exscan(local, wsum, total);
+    if (lo < nbins && above < k_rem && above + local >= k_rem) {
+      for (int b = lo + per - 1; b >= lo; --b) {
+        const uint32_t c = hist[b];
+        if (above + c >= k_rem) {
+          found[0] = static_cast<uint32_t>(b);
+          found[1] = k_rem - above;
+          break;
+        }
+        above += c;
+      }
+    }
+    __syncthreads();
+    prefix |= found[0] << shift;
+    prefix_mask |= static_cast<uint32_t>(nbins - 1) << shift;
+    k_rem = found[1];
+    hi_bit = shift;
+  }
+  const uint32_t thr = prefix, take_eq = k_rem;
+
+  // ---- emit ----
+  const int chunk = (d_ffn + kCtaSelThreads - 1) / kCtaSelThreads;
+  const int begin = min(tid * chunk, d_ffn), end = min(begin + chunk, d_ffn);
+  uint32_t n_gt = 0, n_eq = 0;
+  for (int i = begin; i < end; ++i) {
+    const uint32_t key = KT::key(raw[i]);
+    n_gt += (key > thr) ? 1u : 0u;
+    n_eq += (key == thr) ? 1u : 0u;
+  }
+  uint32_t total = 0;
+  const uint32_t ex = cta_exscan(n_gt | (n_eq << 16), wsum, total);
+  uint32_t eq_seen = ex >> 16;
+  uint32_t pos = (ex & 0xFFFFu) + min(eq_seen, take_eq);
+  int16_t* idx_row = idx + static_cast<int64_t>(row) * k;
+  Bits* gsel_row = reinterpret_cast<Bits*>(g_sel) + static_cast<int64_t>(row) * k;
+  for (int i = begin; i < end; ++i) {
+    const Bits r = raw[i];
+    const uint32_t key = KT::key(r);
+    bool sel = key > thr;
+    if (key == thr) {
+      sel = eq_seen < take_eq;
+      ++eq_seen;
+    }
+    if (sel) {
+      idx_row[pos] = static_cast<int16_t>(i);
+      gsel_row[pos] = r;
+      ++pos;
+      atomicOr(&bm[i >> 5], 1u << (i & 31));
+    }
+    if (write_s) grow[i] = sel ? KT::bits(silu_round<T>(KT::value(r))) : Bits(0);
+  }
+  if (write_s)
+    for (int i = d_ffn + tid; i < words * 32; i += kCtaSelThreads) grow[i] = Bits(0);
+  __syncthreads();
+  const int wchunk = (words + kCtaSelThreads - 1) / kCtaSelThreads;
+  const int wb = min(tid * wchunk, words), we = min(wb + wchunk, words);
+  uint32_t pc = 0;
+  for (int w = wb; w < we; ++w) pc += __popc(bm[w]);
+  uint32_t tot2 = 0;
+  uint32_t run = cta_exscan(pc, wsum, tot2);
+  for (int w = wb; w < we; ++w) {
+    const uint32_t m = bm[w];
+    bitmap[static_cast<int64_t>(row) * words + w] = m;
+    rank0[static_cast<int64_t>(row) * words + w] = static_cast<uint16_t>(run);
+    run += __popc(m);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // bf16 fast path of the Top-K selection: one warp per token, 16-byte loads of 8 channels per
 // lane (vector v = slot * 32 + lane), packed 16-bit order keys. Needs 16-byte aligned rows padded
 // to 32 * words elements.
 // ------------------------------------------------------------------------------------------
 constexpr int kVecSelWarps = 4;
 constexpr int kVecSelBins = 2048;
+constexpr int kVecSelHistWords = kVecSelBins / 2;   // 16-bit counters, two per word (a row has < 65536 channels)
 
 __device__ __forceinline__ uint32_t keys2_from_bits(uint32_t x) {   // two bf16 patterns -> two order keys
   const uint32_t m = (x >> 15) & 0x00010001u;
@@ -209,7 +349,7 @@ __global__ void __launch_bounds__(kVecSelWarps * 32)
 topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k, int words,
                             int write_s, int16_t* __restrict__ idx, uint16_t* __restrict__ g_sel,
                             uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
-  __shared__ uint32_t hist_all[kVecSelWarps][kVecSelBins];
+  __shared__ uint32_t hist_all[kVecSelWarps][kVecSelHistWords];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kVecSelWarps + warp;
   if (row >= tokens) return;   // whole warps leave; only warp-level synchronisation below
@@ -222,7 +362,7 @@ topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, i
   // ---- digit 1: the upper 11 key bits ----
   {
     uint4* h4 = reinterpret_cast<uint4*>(hist);
-    for (int i = lane; i < kVecSelBins / 4; i += 32) h4[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = lane; i < kVecSelHistWords / 4; i += 32) h4[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   __syncwarp();
 #pragma unroll 2
@@ -233,8 +373,9 @@ topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, i
     if (v * 8 < d_ffn) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        atomicAdd(&hist[(a[j] & 0xFFFFu) >> 5], 1u);
-        atomicAdd(&hist[a[j] >> 21], 1u);
+        const uint32_t b0 = (a[j] & 0xFFFFu) >> 5, b1 = a[j] >> 21;
+        atomicAdd(&hist[b0 >> 1], (b0 & 1u) ? 0x10000u : 1u);
+        atomicAdd(&hist[b1 >> 1], (b1 & 1u) ? 0x10000u : 1u);
       }
     }
   }
@@ -242,18 +383,22 @@ topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, i
   uint32_t k_rem = static_cast<uint32_t>(k);
   uint32_t digit1, digit2;
   {
-    // lane l sums the 64 bins [lo, lo + 64) counted from the top (rotated start: no bank conflicts)
+    // lane l sums the 64 bins [lo, lo + 64) counted from the top = 32 words (rotated start: no bank conflicts)
     const int lo = (31 - lane) * 64;
     uint32_t local = 0;
 #pragma unroll 8
-    for (int j = 0; j < 64; ++j) local += hist[lo + ((j + lane) & 63)];
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t w = hist[(lo >> 1) + ((j + lane) & 31)];
+      local += (w & 0xFFFFu) + (w >> 16);
+    }
     uint32_t total;
     const uint32_t above = warp_exscan(local, total);
     const bool mine = above < k_rem && above + local >= k_rem;
     const int src = __ffs(__ballot_sync(0xFFFFFFFFu, mine)) - 1;
     const uint32_t above_src = __shfl_sync(0xFFFFFFFFu, above, src);
     const int top = (31 - src) * 64 + 63;            // highest bin of the owning range
-    const uint32_t c0 = hist[top - 2 * lane], c1 = hist[top - 2 * lane - 1];
+    const uint32_t cw = hist[(top - 2 * lane) >> 1];              // bins top-2l (odd, upper half) and top-2l-1
+    const uint32_t c0 = cw >> 16, c1 = cw & 0xFFFFu;
     const uint32_t ex = warp_exscan(c0 + c1, total) + above_src;
     const bool hit = ex < k_rem && ex + c0 + c1 >= k_rem;
     uint32_t d = 0, nk = 0;
@@ -581,6 +726,26 @@ int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
     return kErrInvalidArg;
   }
   prof_mark(kProfTopk, stream);
+  if (tokens <= 1024) {   // few rows: one CTA per row
+    const size_t esz = dtype == kBF16 ? 2 : 4;
+    const size_t smem = sizeof(uint32_t) * (kCtaSelBins + words) + esz * d_ffn;
+    if (dtype == kBF16) {
+      auto kern = topk_select_cta_kernel<__nv_bfloat16>;
+      if (smem > 48 * 1024 &&
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+        return check_last("topk_select smem attribute");
+      kern<<<tokens, kCtaSelThreads, smem, stream>>>(static_cast<__nv_bfloat16*>(g), ldg, d_ffn, k, words, write_s, idx,
+                                                     static_cast<__nv_bfloat16*>(g_sel), bitmap, rank0);
+    } else {
+      auto kern = topk_select_cta_kernel<float>;
+      if (smem > 48 * 1024 &&
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+        return check_last("topk_select smem attribute");
+      kern<<<tokens, kCtaSelThreads, smem, stream>>>(static_cast<float*>(g), ldg, d_ffn, k, words, write_s, idx,
+                                                     static_cast<float*>(g_sel), bitmap, rank0);
+    }
+    return check_last("topk_select");
+  }
   // bf16 fast path: needs aligned rows padded to the mask width
   if (dtype == kBF16 && ldg >= static_cast<int64_t>(words) * 32 && ldg % 8 == 0 &&
       (reinterpret_cast<uintptr_t>(g) & 15u) == 0) {

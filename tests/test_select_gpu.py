@@ -96,3 +96,14 @@ def test_select_2of8(dtype, tokens, d_ffn):
     _check(g, None, rule="2of8")
     gi = torch.randint(-1, 2, (tokens, d_ffn), generator=torch.Generator().manual_seed(1)).to(dtype)
     _check(gi, None, rule="2of8")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tokens,d_ffn,k", [(1100, 173, 40), (1030, 1376, 256), (1025, 5461, 1024)])
+def test_topk_many_rows(dtype, tokens, d_ffn, k):
+    """More than 1024 rows: the one-warp-per-row kernels (generic, and the bf16 vector path on padded rows)
+    instead of the one-CTA-per-row kernel that small calls use."""
+    g = torch.randn(tokens, d_ffn, generator=torch.Generator().manual_seed(tokens)).to(dtype)
+    g[3, : d_ffn // 2] = 0.25                      # a row that ties heavily at the threshold
+    _check(g, k)
+    _check(g, k, ld=_lib.lib().moc_ffn_ld(d_ffn))
