@@ -2,10 +2,10 @@
 tokens, parameter gradients are summed (averaged) across ranks with one all-reduce per weight.
 
 The reference has no distributed code; the FFN is token-wise, so forward and dX need no
-communication and only dW_gate, dW_up, dW_down are reduced. ``moc_ffn_bwd`` records an event as
-soon as each weight gradient is final (dW_down first), and ``GradAllReducer`` starts that
-tensor's all-reduce on a side stream behind the event, so the transfer overlaps the remaining
-backward GEMMs. Works with any ``torch.distributed`` backend (NCCL over NVLink on GPUs; gloo in
+communication and only dW_gate, dW_up, dW_down are reduced. ``GradAllReducer`` starts the three
+all-reduces on a side stream behind an event of the backward pass: by default the event after its
+last kernel; with ``overlap=True`` the event that ``moc_ffn_bwd`` records as soon as the
+weight-gradient GEMM is done, so that the transfers run beside the dX GEMM. Works with any ``torch.distributed`` backend (NCCL over NVLink on GPUs; gloo in
 the CPU tests of the bookkeeping).
 """
 from __future__ import annotations
@@ -35,9 +35,12 @@ class GradAllReducer:
         # leaving the block waits (stream-wise, not host-wise) for all reductions
     """
 
-    def __init__(self, group=None, average: bool = True):
+    def __init__(self, group=None, average: bool = True, overlap: bool = False):
         self.group = group
         self.average = average
+        # overlap=True starts the reductions behind the weight-gradient GEMM, beside the dX GEMM; the default
+        # starts them after the backward pass (see moc_b200.ffn._grad_ready_early for the measurement)
+        self.overlap = overlap
         self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() else None
         self.launched = 0
 
@@ -68,7 +71,7 @@ class GradAllReducer:
 
     def __enter__(self):
         self.launched = 0
-        _ffn.set_grad_ready_hook(self._on_grad_ready)
+        _ffn.set_grad_ready_hook(self._on_grad_ready, early=self.overlap)
         return self
 
     def __exit__(self, *exc):

@@ -133,11 +133,17 @@ def _maybe_check_status(ws: torch.Tensor, dev) -> None:
 # name in ("down", "gate", "up") right after the backward kernels were enqueued; `event` is
 # recorded on the compute stream at the point where `grad` is final. See moc_b200.dp.
 _grad_ready_hook = None
+# True: events fire as soon as the weight-gradient GEMM is done, so a reduction can run beside the dX GEMM.
+# False (default): one event after the whole backward pass. Measured on 2 x B200: a collective running beside
+# the persistent, statically scheduled dX GEMM delays some of its CTAs and doubles its duration (0.55 -> 1.04 ms),
+# far more than the 0.15 ms the all-reduce of the three gradients takes on NVLink when it runs alone.
+_grad_ready_early = False
 
 
-def set_grad_ready_hook(hook) -> None:
-    global _grad_ready_hook
+def set_grad_ready_hook(hook, early: bool = False) -> None:
+    global _grad_ready_hook, _grad_ready_early
     _grad_ready_hook = hook
+    _grad_ready_early = bool(early)
 
 
 class _MoCB200Function(torch.autograd.Function):
@@ -187,7 +193,7 @@ class _MoCB200Function(torch.autograd.Function):
         go = grad_out.reshape(-1, grad_out.shape[-1]).to(x2d.dtype).contiguous()
         hook = _grad_ready_hook
         events = None
-        if hook is not None:
+        if hook is not None and _grad_ready_early:
             events = tuple(torch.cuda.Event() for _ in range(3))
             for ev in events:
                 ev.record()   # PyTorch creates the CUDA event lazily; the library re-records it
@@ -196,6 +202,10 @@ class _MoCB200Function(torch.autograd.Function):
         d_gate = d_gate.to(ctx.w_dtypes[0])
         d_up = d_up.to(ctx.w_dtypes[1])
         d_down = d_down.to(ctx.w_dtypes[2])
+        if hook is not None and events is None:
+            done = torch.cuda.Event()
+            done.record()          # after the last backward kernel
+            events = (done, done, done)
         if hook is not None:
             hook("down", d_down, events[0])
             hook("gate", d_gate, events[1])
