@@ -179,6 +179,7 @@ class _MoCB200Function(torch.autograd.Function):
             saved += [s_sel, z_sel]
         ctx.save_for_backward(*saved)
         ctx.recompute_sz = recompute_sz
+        ctx.set_materialize_grads(False)   # no zero-filled gradient tensor for the integer index output
         ctx.x_shape = x.shape
         ctx.x_dtype = x.dtype
         ctx.w_dtypes = (gate_w.dtype, up_w.dtype, down_w.dtype)
@@ -187,6 +188,8 @@ class _MoCB200Function(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out, _grad_idx):
+        if grad_out is None:
+            return (None,) * 8
         saved = ctx.saved_tensors
         x2d, gw, uw, down_w_t, idx, g_sel, u_sel = saved[:7]
         s_sel, z_sel = (None, None) if ctx.recompute_sz else saved[7:9]
