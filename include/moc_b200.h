@@ -82,7 +82,8 @@ int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64
 /* C[m, n] = A[m, k] * B[n, k]^T with fp32 accumulation. a_mn / b_mn = 1 when the operand is
  * stored [k][m] / [k][n] (M or N contiguous) instead of [m][k] / [n][k]. c_transposed = 1
  * stores C^T (C[j * ldc + i]). impl: 0 = default core of the dtype (bf16: tcgen05 / TMEM,
- * f32: CUDA cores), 1 = CUDA-core core for either dtype. status: one device int, zeroed by
+ * CTA-pair kernel when m > 128, else the single-CTA kernel; f32: CUDA cores), 1 = CUDA-core
+ * core for either dtype, 2 / 3 = force the CTA-pair / single-CTA tensor-core kernel (bf16). status: one device int, zeroed by
  * the caller, receives a code if a bounded device-side wait gives up. Stands in for the
  * `@` / nn.Linear calls of moc/ffn.py:141-163, :203-254. */
 int moc_gemm(int dtype, int impl, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_mn,

@@ -6,6 +6,7 @@
 #include <cudaTypedefs.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -14,6 +15,7 @@
 #include "epilogues.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 #include "internal.h"
 
 namespace moc {
@@ -178,6 +180,73 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
   return check_last("gemm_tcgen05");
 }
 
+// CTA-pair variant (cta_group::2): 256 x 256 tiles per cluster of two CTAs.
+template <class Epi>
+static int launch_tcgen05_pair(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
+  GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const int nmaps = p.k1 > 0 ? 2 : p.groups;
+  int rc;
+  for (int i = 0; i < nmaps; ++i) {
+    const int kext = (p.k1 > 0 && i == 1) ? p.k1 : p.k0;
+    if ((rc = make_operand_map(&maps.a[i], p.a[i], p.m, kext, kBlockM)) != kOk) return rc;
+    if ((rc = make_operand_map(&maps.b[i], p.b[i], p.n, kext, kBlockN / 2)) != kOk) return rc;
+    if (p.a[i].mn_major != p.a[0].mn_major || p.b[i].mn_major != p.b[0].mn_major) {
+      set_error("all K segments / groups of one launch must use the same operand majors");
+      return kErrUnsupported;
+    }
+  }
+  GemmShape sh;
+  sh.m = p.m;
+  sh.n = p.n;
+  sh.kb0 = ceil_div_i(p.k0, kBlockK);
+  sh.kb1 = p.k1 > 0 ? ceil_div_i(p.k1, kBlockK) : 0;
+  sh.groups = p.groups;
+  sh.a_mn = p.a[0].mn_major;
+  sh.b_mn = p.b[0].mn_major;
+  sh.tiles_m = ceil_div_i(p.m, 2 * kBlockM);   // 256-row tile pairs
+  sh.tiles_n = ceil_div_i(p.n, kBlockN);
+  sh.status = p.status;
+  auto kern = gemm_tcgen05_pair_kernel<Epi>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
+    return check_last("gemm pair smem attribute");
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_clusters = n;
+  }
+  const int tiles = sh.tiles_m * sh.tiles_n * sh.groups;
+  const int pairs = tiles < max_clusters ? tiles : max_clusters;
+  prof_mark(kProfGemmTc, stream);
+  kern<<<2 * pairs, kGemmThreads, kPairSmemBytes, stream>>>(maps, sh, epi);
+  return check_last("gemm_tcgen05_pair");
+}
+
+// MOC_B200_GEMM_PAIR=0 in the environment keeps every launch on the single-CTA kernel (a switch for A/B timing).
+static bool pair_kernel_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MOC_B200_GEMM_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 template <typename T>
 static SimtOperand<T> simt_operand(const MatOperand& op) {
   SimtOperand<T> o;
@@ -206,6 +275,14 @@ static int launch_simt(const GemmProblem& p, const Epi& epi, cudaStream_t stream
 template <class Epi>
 static int launch_core_bf16(const GemmProblem& p, const Epi& epi, cudaStream_t stream) {
   if (p.impl == 1) return launch_simt<__nv_bfloat16, Epi>(p, epi, stream);
+  if (!p.status) {
+    set_error("tcgen05 GEMM needs a device status word");
+    return kErrInvalidArg;
+  }
+  // A pair of CTAs shares each 256-column B tile, which cuts the operand bytes an SM pulls from L2 per flop by a
+  // third; with a single 128-row tile in M the second CTA would only multiply padding.
+  if (p.impl == 2 || (p.impl == 0 && p.m > kBlockM && pair_kernel_enabled()))
+    return launch_tcgen05_pair<Epi>(p, epi, stream);
   return launch_tcgen05<Epi>(p, epi, stream);
 }
 

@@ -56,20 +56,26 @@ CASES = [
     (1, 8, 8),
     (3, 5461, 2048),     # odd N (d_ffn of the 1b preset), tiny M
     (640, 384, 5461),    # odd K
+    (1000, 777, 1200),   # several 256-row tile pairs with a tail in each dimension
 ]
+
+# bf16 tensor-core cores: 0 = automatic choice, 2 = CTA-pair kernel (256-row tiles), 3 = single-CTA kernel
+TC_IMPLS = [0, 2, 3]
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
 @pytest.mark.parametrize("m,n,k", CASES)
-def test_tcgen05_gemm_bf16(m, n, k, a_mn, b_mn):
-    got, ref = _run_gemm(torch.bfloat16, 0, m, n, k, a_mn, b_mn, 0, seed=m + n + k)
+@pytest.mark.parametrize("impl", TC_IMPLS)
+def test_tcgen05_gemm_bf16(impl, m, n, k, a_mn, b_mn):
+    got, ref = _run_gemm(torch.bfloat16, impl, m, n, k, a_mn, b_mn, 0, seed=m + n + k)
     assert torch.isfinite(got).all()
     torch.testing.assert_close(got, ref.bfloat16().float(), rtol=2 ** -7, atol=1e-2 * max(1.0, (k / 64) ** 0.5))
 
 
 @pytest.mark.parametrize("m,n,k", [(130, 300, 100), (256, 512, 320)])
-def test_tcgen05_gemm_transposed_store(m, n, k):
-    got, ref = _run_gemm(torch.bfloat16, 0, m, n, k, 1, 1, 1, seed=7)
+@pytest.mark.parametrize("impl", TC_IMPLS)
+def test_tcgen05_gemm_transposed_store(impl, m, n, k):
+    got, ref = _run_gemm(torch.bfloat16, impl, m, n, k, 1, 1, 1, seed=7)
     torch.testing.assert_close(got, ref.bfloat16().float(), rtol=2 ** -7, atol=2e-2)
 
 
@@ -83,10 +89,19 @@ def test_simt_gemm(dtype, a_mn, b_mn, c_t):
         torch.testing.assert_close(got, ref.bfloat16().float(), rtol=2 ** -7, atol=2e-2)
 
 
-def test_tcgen05_matches_simt_bitwise_class():
+def test_pair_and_single_cta_kernels_agree_bitwise():
+    """Both tensor-core kernels add the same K blocks in the same order into fp32 TMEM accumulators, so their
+    bf16 results are identical bit for bit."""
+    a, _ = _run_gemm(torch.bfloat16, 2, 1000, 777, 1200, 0, 1, 0, seed=13)
+    b, _ = _run_gemm(torch.bfloat16, 3, 1000, 777, 1200, 0, 1, 0, seed=13)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("impl", TC_IMPLS)
+def test_tcgen05_matches_simt_bitwise_class(impl):
     """Same bf16 inputs through both cores: both accumulate in fp32, results may differ only by
     the final rounding of slightly different fp32 sums."""
-    a, ref = _run_gemm(torch.bfloat16, 0, 256, 512, 512, 0, 0, 0, seed=11)
+    a, ref = _run_gemm(torch.bfloat16, impl, 256, 512, 512, 0, 0, 0, seed=11)
     b, _ = _run_gemm(torch.bfloat16, 1, 256, 512, 512, 0, 0, 0, seed=11)
     diff = (a - b).abs()
     assert (diff > 0).float().mean().item() < 0.05
