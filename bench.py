@@ -406,8 +406,11 @@ def run_ours(args, rank, world, local_rank):
         # Software pipeline over steps, as an input pipeline would run it: the host->device copy of step i+1
         # and the device->host copy of step i-1 overlap the kernels of step i (two device buffer sets, one
         # copy stream per direction). Every copy of every step is inside the timed region.
-        y_host = [torch.empty_like(x_host) for _ in range(2)]
-        dx_host = [torch.empty_like(x_host) for _ in range(2)]
+        # empty_like does not inherit the pinned property; a pageable destination would make every result copy
+        # synchronous and staged
+        y_host = [torch.empty(x_host.shape, dtype=x_host.dtype, pin_memory=True) for _ in range(2)]
+        dx_host = [torch.empty(x_host.shape, dtype=x_host.dtype, pin_memory=True) for _ in range(2)]
+        assert x_host.is_pinned() and dy_host.is_pinned() and y_host[0].is_pinned() and dx_host[0].is_pinned()
         x_dev = [torch.empty_like(x).requires_grad_(True) for _ in range(2)]
         dy_dev = [torch.empty_like(dy) for _ in range(2)]
         in_ready = [torch.cuda.Event() for _ in range(2)]
