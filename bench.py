@@ -362,7 +362,7 @@ def run_ours(args, rank, world, local_rank):
 
     # per-kernel durations from the event profile
     kinds = {1: "gemm_tcgen05", 2: "gemm_simt", 3: "topk_select", 4: "select_2of8", 5: "expand_z", 6: "transpose",
-             12: "bwd_sparse", 13: "gather_sel"}
+             12: "bwd_sparse"}
     per_kind = {}
     launches = 0
     for i in range(min(n_prof, cap) - 1):

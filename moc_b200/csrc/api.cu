@@ -115,8 +115,8 @@ int moc_topk_select(int dtype, const void* g, int64_t ldg, int64_t tokens, int64
     set_error("moc_topk_select: null pointer or ldg < d_ffn");
     return kErrInvalidArg;
   }
-  return launch_topk_select(dtype, const_cast<void*>(g), ldg, (int)tokens, (int)d_ffn, (int)k, 0, idx, g_sel, bitmap,
-                            rank0, as_stream(stream));
+  return launch_topk_select(dtype, const_cast<void*>(g), ldg, (int)tokens, (int)d_ffn, (int)k, nullptr, idx, g_sel,
+                            bitmap, rank0, as_stream(stream));
 }
 
 int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64_t d_ffn, int16_t* idx, void* g_sel,
@@ -128,8 +128,8 @@ int moc_select_2of8(int dtype, const void* g, int64_t ldg, int64_t tokens, int64
     set_error("moc_select_2of8: null pointer or ldg < d_ffn");
     return kErrInvalidArg;
   }
-  return launch_select_2of8(dtype, const_cast<void*>(g), ldg, (int)tokens, (int)d_ffn, 0, idx, g_sel, bitmap, rank0,
-                            as_stream(stream));
+  return launch_select_2of8(dtype, const_cast<void*>(g), ldg, (int)tokens, (int)d_ffn, nullptr, idx, g_sel, bitmap,
+                            rank0, as_stream(stream));
 }
 
 int moc_gemm(int dtype, int impl, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, int a_mn,
@@ -183,34 +183,33 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   const int64_t ld = ffn_ld(d_ffn);
   const int words = (int)mask_words(d_ffn);
 
-  // G = X Wg^T (moc/ffn.py:141), rounded to the storage type, rows padded to ld
+  // G = X Wg^T and U = X Wu^T (moc/ffn.py:141, :146) in one grouped launch, both rounded to the storage type,
+  // rows padded to ld
+  void* u_dense = static_cast<uint8_t*>(dense) + round_up_i64(tokens * ld * (int64_t)esize(dtype), 256);
   GemmProblem p = problem(dtype, status, tokens, d_ffn, d);
+  p.groups = 2;
   p.a[0] = operand(x, d, 0);
   p.b[0] = operand(w_gate, d, 0);
-  p.epi = store_epi(dense, ld, 0);
-  if ((rc = launch_gemm(p, stream)) != kOk) return rc;
-
-  // channel selection on the rounded G (moc/ffn.py:144-147); G becomes S' = mask * SiLU(G) (moc/ffn.py:157)
-  if (select == MOC_SELECT_TOPK)
-    rc = launch_topk_select(dtype, dense, ld, (int)tokens, (int)d_ffn, (int)k, 1, idx, g_sel, bitmap, rank0, stream);
-  else
-    rc = launch_select_2of8(dtype, dense, ld, (int)tokens, (int)d_ffn, 1, idx, g_sel, bitmap, rank0, stream);
-  if (rc != kOk) return rc;
-
-  // U = X Wu^T; the epilogue turns S' into Z' = S' * U in place and keeps the rounded U row (moc/ffn.py:146-161)
-  void* u_dense = static_cast<uint8_t*>(dense) + round_up_i64(tokens * ld * (int64_t)esize(dtype), 256);
-  p.b[0] = operand(w_up, d, 0);
+  p.a[1] = operand(x, d, 0);
+  p.b[1] = operand(w_up, d, 0);
   p.epi = EpiArgs{};
-  p.epi.kind = kEpiUpGated;
-  p.epi.dense0 = dense;
-  p.epi.dense1 = u_dense;
-  p.epi.ld_dense = ld;
+  p.epi.kind = kEpiStore;
+  p.epi.c[0] = dense;
+  p.epi.ldc[0] = ld;
+  p.epi.c[1] = u_dense;
+  p.epi.ldc[1] = ld;
   if ((rc = launch_gemm(p, stream)) != kOk) return rc;
 
-  // compact saved set: the selected channels of U (and, on request, s and z) (moc/ffn.py:156, :166-169)
-  if ((rc = launch_gather_sel(dtype, idx, u_dense, dense, g_sel, u_sel, s_sel, z_sel, ld, (int)tokens, (int)k,
-                              stream)) != kOk)
-    return rc;
+  // channel selection on the rounded G (moc/ffn.py:144-147); the same kernel gathers the selected channels of U
+  // into the compact saved set and turns the G rows into Z' = mask * round(round(SiLU(G)) * U) in place
+  // (moc/ffn.py:156-161, :166-169)
+  SelectFuse fuse{u_dense, u_sel, s_sel, z_sel};
+  if (select == MOC_SELECT_TOPK)
+    rc = launch_topk_select(dtype, dense, ld, (int)tokens, (int)d_ffn, (int)k, &fuse, idx, g_sel, bitmap, rank0,
+                            stream);
+  else
+    rc = launch_select_2of8(dtype, dense, ld, (int)tokens, (int)d_ffn, &fuse, idx, g_sel, bitmap, rank0, stream);
+  if (rc != kOk) return rc;
 
   // Y = Z' Wd^T (moc/ffn.py:163): A = Z' [tokens, F] K-major, B = W_down^T [F, d] N-contiguous
   GemmProblem q = problem(dtype, status, tokens, d, d_ffn);

@@ -462,10 +462,10 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
     return rc;
   }
   if (rule == 0)
-    rc = launch_topk_select(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, (int)k, 0, w.idx, w.g_sel, w.bitmap,
+    rc = launch_topk_select(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, (int)k, nullptr, w.idx, w.g_sel, w.bitmap,
                             w.rank0, stream);
   else
-    rc = launch_select_2of8(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, 0, w.idx, w.g_sel, w.bitmap, w.rank0,
+    rc = launch_select_2of8(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, nullptr, w.idx, w.g_sel, w.bitmap, w.rank0,
                             stream);
   if (rc != kOk) return rc;
   rc = selected_tail(w, xb, static_cast<const bf16*>(w_up), static_cast<const bf16*>(w_down_t),

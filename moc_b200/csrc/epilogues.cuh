@@ -133,43 +133,6 @@ struct EpiStore {
   }
 };
 
-// ---- forward: up projection x selected SiLU(gate) ------------------------------------------
-// acc = U tile. The selection kernel has already replaced the dense gate row by
-// S' = mask * round(SiLU(G)) (zero outside the selected channels, moc/ffn.py:157). The epilogue
-// rounds u = round(U) (the reference's U is a stored tensor, moc/ffn.py:146), writes
-// z = round(S' * u) over the S' chunk in place - the zero-filled Z' that the down projection
-// consumes (moc/ffn.py:158-163) - and the dense u row to a second scratch matrix, from which
-// gather_sel_kernel picks the selected channels into the compact saved set (moc/ffn.py:156).
-template <typename T>
-struct EpiUpGated {
-  struct Ctx {
-    uint4 s[Chunk32<T>::kVecs];
-  };
-  T* sz;        // in: S' [tokens, ld]; out: Z' [tokens, ld]
-  T* u_out;     // out: round(U) [tokens, ld]
-  int64_t ld;
-
-  __device__ __forceinline__ void begin(Ctx&, int, int, int, int) const {}
-  __device__ __forceinline__ void prefetch(Ctx& ctx, int row, int col0, int) const {
-    Chunk32<T>::load_raw(sz + static_cast<int64_t>(row) * ld + col0, ctx.s);
-  }
-  __device__ __forceinline__ void operator()(Ctx& ctx, int, int row, int col0, int, const float (&acc)[32]) const {
-    float s[32], u[32], out[32];
-    Chunk32<T>::unpack(ctx.s, s);
-#pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-      u[j] = acc[j];
-      u[j + 1] = acc[j + 1];
-      Num<T>::round_pair(u[j], u[j + 1]);
-      out[j] = s[j] * u[j];
-      out[j + 1] = s[j + 1] * u[j + 1];
-    }
-    const int64_t off = static_cast<int64_t>(row) * ld + col0;
-    Chunk32<T>::store_rounded(u_out + off, u);
-    Chunk32<T>::store(sz + off, out);   // the packed store conversion is the rounding of z
-  }
-};
-
 // ---- dense SwiGLU forward: acc = U tile, Z = round(round(SiLU(G)) * round(U)) ------------
 // (moc/ffn.py:120-121). Reads G, writes U (kept for the backward pass) and Z.
 template <typename T>

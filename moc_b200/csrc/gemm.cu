@@ -315,17 +315,6 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
       epi.n = p.n;
       return run(epi);
     }
-    case kEpiUpGated: {
-      if (!dense_ok || !e.dense0 || !e.dense1) {
-        set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 128");
-        return kErrWorkspace;
-      }
-      EpiUpGated<T> epi;
-      epi.sz = static_cast<T*>(e.dense0);
-      epi.u_out = static_cast<T*>(e.dense1);
-      epi.ld = e.ld_dense;
-      return run(epi);
-    }
     case kEpiDenseSwiGLU: {
       if (!dense_ok) {
         set_error("dense scratch must be 16-byte aligned with a leading dimension that is a multiple of 128");

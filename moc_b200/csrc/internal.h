@@ -14,7 +14,7 @@ struct MatOperand {
   int mn_major;   // 0: memory is [mn][k] (K contiguous); 1: memory is [k][mn] (M/N contiguous)
 };
 
-enum EpiKind : int { kEpiStore = 0, kEpiUpGated = 1, kEpiDenseSwiGLU = 2 };
+enum EpiKind : int { kEpiStore = 0, kEpiDenseSwiGLU = 2 };
 
 constexpr int kGemmMaxGroups = 3;
 
@@ -24,7 +24,6 @@ struct EpiArgs {
   void* c[kGemmMaxGroups];
   int64_t ldc[kGemmMaxGroups];
   int transposed[kGemmMaxGroups];
-  // kEpiUpGated: dense0 = S' -> Z' in place, dense1 = U (out).
   // kEpiDenseSwiGLU: dense0 = G (in), dense1 = U (out), dense2 = Z (out)
   void* dense0;
   void* dense1;
@@ -49,18 +48,23 @@ struct GemmProblem {
 int launch_gemm(const GemmProblem& p, cudaStream_t stream);
 
 // ---- selection / auxiliary kernels (kernels.cu) ---------------------------------------------
-// write_s != 0: the gate rows (ldg >= ffn_ld) are overwritten in place by S' = mask * round(SiLU(g))
-int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, int write_s, int16_t* idx,
+// Optional forward fusion of a selection launch: with `fuse` set the kernel also gathers u = U[t, ch] of every
+// selected channel from the dense rows u_dense (same leading dimension as g), writes u_sel (and s_sel =
+// round(SiLU(g)), z_sel = round(s * u) when set) and overwrites the gate rows (ldg >= ffn_ld) in place by
+// Z' = mask * z.
+struct SelectFuse {
+  const void* u_dense;
+  void* u_sel;
+  void* s_sel;   // may be null
+  void* z_sel;   // may be null
+};
+int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, const SelectFuse* fuse,
+                       int16_t* idx, void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
+int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, const SelectFuse* fuse, int16_t* idx,
                        void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
-int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int write_s, int16_t* idx, void* g_sel,
-                       uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
 // Z'[tokens, ld] <- zero-filled scatter of the compact z (or of round(round(SiLU(g)) * u) when z_sel is null)
 int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void* g_sel, const void* u_sel, void* dense,
                     int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
-// compact saved set from dense rows: u_sel[t, p] = u_dense[t, idx[t, p]]; optional s_sel = round(SiLU(g_sel)),
-// z_sel[t, p] = z_dense[t, idx[t, p]]
-int launch_gather_sel(int dtype, const int16_t* idx, const void* u_dense, const void* z_dense, const void* g_sel,
-                      void* u_sel, void* s_sel, void* z_sel, int64_t ld, int tokens, int k, cudaStream_t stream);
 // dZ[tokens, ld] (in) -> dG' (grad_g_out) and dU' (written over dZ in place): gather, SiLU', zero fill
 int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
                       void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
@@ -78,7 +82,7 @@ int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_
 enum ProfTag : int {
   kProfEnd = 0, kProfGemmTc = 1, kProfGemmSimt = 2, kProfTopk = 3, kProfSel2of8 = 4, kProfExpand = 5,
   kProfTranspose = 6, kProfDecodeGate = 7, kProfDecodeUp = 8, kProfDecodeDown = 9, kProfDecodeFused28 = 10,
-  kProfDecodeDense = 11, kProfBwdSparse = 12, kProfGatherSel = 13,
+  kProfDecodeDense = 11, kProfBwdSparse = 12,
 };
 void prof_mark(int tag, cudaStream_t stream);
 

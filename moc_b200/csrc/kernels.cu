@@ -6,8 +6,10 @@
 //                        radix *select*: one warp per token finds the K-th largest order key
 //                        digit by digit (11-bit shared-memory histograms), ties at the threshold
 //                        go to the lower channel index, and the selected set is emitted in
-//                        ascending channel order together with a bitmap. On request the gate row
-//                        is overwritten by S' = mask * SiLU(G) for the up-projection epilogue.
+//                        ascending channel order together with a bitmap. On request the same
+//                        kernel gathers the selected channels of the dense U rows into the compact
+//                        saved set and overwrites the gate row by Z' = mask * round(SiLU(G)) * U,
+//                        the operand of the down projection (moc/ffn.py:156-163).
 //   select_2of8_kernel : structured top-2 of every 8 consecutive channels (moc/ffn.py:68-108).
 //   expand_z_kernel    : compact z -> zero-filled dense Z' (moc/ffn.py:196-199, :435-442).
 //   bwd_sparse_kernel  : dense dZ -> zero-filled dense dG', dU' through the selected channels
@@ -51,13 +53,38 @@ __device__ __forceinline__ uint32_t hist_count(const uint32_t* hist, int b) {
   return (hist[b >> 1] >> ((b & 1) * 16)) & 0xFFFFu;
 }
 
+// Forward fusion of the selection kernels. With u_dense set (rows of ldg elements like g), a kernel
+// also gathers u = U[row, ch] of every selected channel, stores it in the compact saved set (with
+// s = round(SiLU(g)) and z = round(s * u) on request) and overwrites the row of g in place by
+// Z' = selected ? z : 0 over the full padded width 32 * words (moc/ffn.py:156-161).
+template <typename T>
+struct SelFuseT {
+  const T* u_dense;
+  T* u_sel;
+  T* s_sel;
+  T* z_sel;
+};
+
+// One selected channel: returns the bits of z for the dense row, writes the compact outputs.
+template <typename T>
+__device__ __forceinline__ typename KeyTraits<T>::Bits fuse_point(const SelFuseT<T>& f, int64_t dense_off,
+                                                                  int64_t compact_off, float gv) {
+  const T u = f.u_dense[dense_off];
+  float sv, zv;
+  moc_fwd_point<T>(gv, Num<T>::to_float(u), sv, zv);
+  f.u_sel[compact_off] = u;
+  if (f.s_sel) f.s_sel[compact_off] = Num<T>::from_float(sv);
+  const T z = Num<T>::from_float(zv);
+  if (f.z_sel) f.z_sel[compact_off] = z;
+  return *reinterpret_cast<const typename KeyTraits<T>::Bits*>(&z);
+}
+
 // One warp per token row; lane l handles the channels l, l + 32, l + 64, ... so that a warp
 // ballot over one step is exactly one 32-channel word of the selection bitmap and channel
-// order equals (step, lane) order. write_s != 0: the row of g is overwritten in place by
-// S' = selected ? round(SiLU(g)) : 0 over the full padded width 32 * words.
+// order equals (step, lane) order.
 template <typename T>
 __global__ void __launch_bounds__(kSelWarpsPerCta * 32)
-topk_select_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k, int words, int write_s,
+topk_select_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k, int words, SelFuseT<T> fuse,
                    int16_t* __restrict__ idx, T* __restrict__ g_sel, uint32_t* __restrict__ bitmap,
                    uint16_t* __restrict__ rank0) {
   using KT = KeyTraits<T>;
@@ -141,12 +168,16 @@ topk_select_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k,
     const uint32_t eq_ballot = __ballot_sync(0xFFFFFFFFu, is_eq);
     const bool sel = valid && (key > thr || (is_eq && eq_seen + __popc(eq_ballot & lt_mask) < take_eq));
     const uint32_t word = __ballot_sync(0xFFFFFFFFu, sel);
+    Bits zbits = Bits(0);
     if (sel) {
       const uint32_t pos = run + __popc(word & lt_mask);
       idx_row[pos] = static_cast<int16_t>(c);
       gsel_row[pos] = raw;
+      if (fuse.u_dense)
+        zbits = fuse_point<T>(fuse, static_cast<int64_t>(row) * ldg + c, static_cast<int64_t>(row) * k + pos,
+                              KT::value(raw));
     }
-    if (write_s) grow[c] = sel ? KT::bits(silu_round<T>(KT::value(raw))) : Bits(0);
+    if (fuse.u_dense) grow[c] = zbits;
     if (lane == 0) {
       bm_row[w] = word;
       rk_row[w] = static_cast<uint16_t>(run);
@@ -189,7 +220,7 @@ __device__ __forceinline__ uint32_t cta_exscan(uint32_t v, uint32_t* wsum /*[kCt
 
 template <typename T>
 __global__ void __launch_bounds__(kCtaSelThreads)
-topk_select_cta_kernel(T* __restrict__ g, int64_t ldg, int d_ffn, int k, int words, int write_s,
+topk_select_cta_kernel(T* __restrict__ g, int64_t ldg, int d_ffn, int k, int words, SelFuseT<T> fuse,
                        int16_t* __restrict__ idx, T* __restrict__ g_sel, uint32_t* __restrict__ bitmap,
                        uint16_t* __restrict__ rank0) {
   using KT = KeyTraits<T>;
@@ -270,15 +301,19 @@ topk_select_cta_kernel(T* __restrict__ g, int64_t ldg, int d_ffn, int k, int wor
       sel = eq_seen < take_eq;
       ++eq_seen;
     }
+    Bits zbits = Bits(0);
     if (sel) {
       idx_row[pos] = static_cast<int16_t>(i);
       gsel_row[pos] = r;
+      if (fuse.u_dense)
+        zbits = fuse_point<T>(fuse, static_cast<int64_t>(row) * ldg + i, static_cast<int64_t>(row) * k + pos,
+                              KT::value(r));
       ++pos;
       atomicOr(&bm[i >> 5], 1u << (i & 31));
     }
-    if (write_s) grow[i] = sel ? KT::bits(silu_round<T>(KT::value(r))) : Bits(0);
+    if (fuse.u_dense) grow[i] = zbits;
   }
-  if (write_s)
+  if (fuse.u_dense)
     for (int i = d_ffn + tid; i < words * 32; i += kCtaSelThreads) grow[i] = Bits(0);
   __syncthreads();
   const int wchunk = (words + kCtaSelThreads - 1) / kCtaSelThreads;
@@ -347,7 +382,7 @@ __device__ __forceinline__ void load_keys8(const uint4* grow4, int v, int nvec, 
 // issue-bound and a fully unrolled body thrashes the instruction cache.
 __global__ void __launch_bounds__(kVecSelWarps * 32)
 topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k, int words,
-                            int write_s, int16_t* __restrict__ idx, uint16_t* __restrict__ g_sel,
+                            SelFuseT<__nv_bfloat16> fuse, int16_t* __restrict__ idx, uint16_t* __restrict__ g_sel,
                             uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
   __shared__ uint32_t hist_all[kVecSelWarps][kVecSelHistWords];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -444,12 +479,19 @@ topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, i
   uint16_t* gsel_row = g_sel + static_cast<int64_t>(row) * k;
   uint32_t* bm_row = bitmap + static_cast<int64_t>(row) * words;
   uint16_t* rk_row = rank0 + static_cast<int64_t>(row) * words;
+  // fused forward: the U row is read with the same coalesced vectors as the gate row and the selected values
+  // go to u_sel beside idx and g_sel, so that the compact pass below needs no scattered reads
+  const uint4* urow4 = reinterpret_cast<const uint4*>(fuse.u_dense + static_cast<int64_t>(row) * ldg);
+  uint16_t* usel_row = reinterpret_cast<uint16_t*>(fuse.u_sel) + static_cast<int64_t>(row) * k;
   uint32_t run = 0, eq_seen = 0;
 #pragma unroll 1
   for (int i = 0; i < nslots; ++i) {
     const int v = i * 32 + lane;
     uint32_t a[4];
     load_keys8(grow4, v, nvec, d_ffn, a);
+    uint4 uv = make_uint4(0u, 0u, 0u, 0u);
+    if (fuse.u_dense && v < nvec) uv = urow4[v];
+    const uint32_t ua[4] = {uv.x, uv.y, uv.z, uv.w};
     uint32_t gtm = 0, eqm = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -481,31 +523,40 @@ topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, i
         const uint32_t key16 = (a[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
         idx_row[pos] = static_cast<int16_t>(8 * v + j);
         gsel_row[pos] = static_cast<uint16_t>(bits_from_key16(key16));
+        if (fuse.u_dense) usel_row[pos] = static_cast<uint16_t>((ua[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
         ++pos;
       }
     }
-    if (write_s && v < nvec) grow4[v] = make_uint4(0u, 0u, 0u, 0u);   // selected channels: filled in below
+    if (fuse.u_dense && v < nvec) grow4[v] = make_uint4(0u, 0u, 0u, 0u);   // selected channels: filled in below
     run += tot_sel;
     eq_seen += tot_eq;
   }
 
-  // ---- S' = round(SiLU(g)) of the selected channels, computed in compact space (full lanes) ----
-  if (write_s) {
+  // ---- Z' and the saved u (s, z) of the selected channels, computed in compact space (full lanes) ----
+  if (fuse.u_dense) {
     __syncwarp();   // orders the zero fill and the compact outputs above before the accesses below
+    uint16_t* ssel_row = fuse.s_sel ? reinterpret_cast<uint16_t*>(fuse.s_sel) + static_cast<int64_t>(row) * k : nullptr;
+    uint16_t* zsel_row = fuse.z_sel ? reinterpret_cast<uint16_t*>(fuse.z_sel) + static_cast<int64_t>(row) * k : nullptr;
+#pragma unroll 4
     for (int p = lane; p < k; p += 32) {
       const int ch = idx_row[p];
       const float gv = __uint_as_float(static_cast<uint32_t>(gsel_row[p]) << 16);
-      const __nv_bfloat16 s = __float2bfloat16_rn(gv * sigmoid_act<__nv_bfloat16>(gv));
-      grow[ch] = *reinterpret_cast<const uint16_t*>(&s);
+      const float uf = __uint_as_float(static_cast<uint32_t>(usel_row[p]) << 16);
+      float sv, zv;
+      moc_fwd_point<__nv_bfloat16>(gv, uf, sv, zv);
+      const uint16_t zb = static_cast<uint16_t>(__float_as_uint(zv) >> 16);   // zv is already a bf16 value
+      grow[ch] = zb;
+      if (ssel_row) ssel_row[p] = static_cast<uint16_t>(__float_as_uint(sv) >> 16);
+      if (zsel_row) zsel_row[p] = zb;
     }
   }
 }
 
 // One thread per (token, 32-channel word) = 4 groups of 8. Lower channel index wins ties
-// (moc/inference/triton_fused_ffn_kernels.py:103-114). write_s: as in topk_select_kernel.
+// (moc/inference/triton_fused_ffn_kernels.py:103-114). fuse: as in topk_select_kernel.
 template <typename T>
 __global__ void select_2of8_kernel(T* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k_eff, int words,
-                                   int write_s, int16_t* __restrict__ idx, T* __restrict__ g_sel,
+                                   SelFuseT<T> fuse, int16_t* __restrict__ idx, T* __restrict__ g_sel,
                                    uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
   using KT = KeyTraits<T>;
   using Bits = typename KT::Bits;
@@ -557,10 +608,16 @@ __global__ void select_2of8_kernel(T* __restrict__ g, int64_t ldg, int tokens, i
       mask |= 1u << (q * 8 + lo);
       if (hi >= 0) mask |= 1u << (q * 8 + hi);
     }
-    if (write_s) {
+    if (fuse.u_dense) {
+      const int pos = (c0 >> 3) * 2;
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        grow[c0 + j] = (j == lo || j == hi) ? KT::bits(silu_round<T>(KT::value(raw[j]))) : Bits(0);
+      for (int j = 0; j < 8; ++j) {
+        Bits zbits = Bits(0);
+        if (j == lo || j == hi)
+          zbits = fuse_point<T>(fuse, static_cast<int64_t>(row) * ldg + c0 + j,
+                                static_cast<int64_t>(row) * k_eff + pos + (j == hi ? 1 : 0), KT::value(raw[j]));
+        grow[c0 + j] = zbits;
+      }
     }
   }
   bitmap[gid] = mask;
@@ -611,32 +668,6 @@ expand_z_kernel(const int16_t* __restrict__ idx, const T* __restrict__ z_sel, co
   }
   __syncthreads();
   row_store(zrow, dense + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
-}
-
-// Compact saved set of the forward pass: u_sel[p] = U[token, idx[p]] from the dense rounded U row;
-// on request s_sel[p] = round(SiLU(g_sel[p])) and z_sel[p] = Z'[token, idx[p]] (moc/ffn.py:156-158).
-template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
-gather_sel_kernel(const int16_t* __restrict__ idx, const T* __restrict__ u_dense, const T* __restrict__ z_dense,
-                  const T* __restrict__ g_sel, T* __restrict__ u_sel, T* __restrict__ s_sel, T* __restrict__ z_sel,
-                  int64_t ld, int k) {
-  extern __shared__ __align__(16) uint8_t row_smem[];
-  T* urow = reinterpret_cast<T*>(row_smem);
-  const int row = blockIdx.x;
-  const int64_t crow = static_cast<int64_t>(row) * k;
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(u_dense + static_cast<int64_t>(row) * ld);
-    uint4* dst = reinterpret_cast<uint4*>(urow);
-    const int nvec = static_cast<int>(ld) * static_cast<int>(sizeof(T)) / 16;
-    for (int v = threadIdx.x; v < nvec; v += kRowThreads) dst[v] = src[v];
-  }
-  __syncthreads();
-  for (int p = threadIdx.x; p < k; p += kRowThreads) {
-    const int ch = idx[crow + p];
-    u_sel[crow + p] = urow[ch];
-    if (s_sel) s_sel[crow + p] = Num<T>::from_float(silu_round<T>(Num<T>::to_float(g_sel[crow + p])));
-    if (z_sel) z_sel[crow + p] = z_dense[static_cast<int64_t>(row) * ld + ch];
-  }
 }
 
 // dZ (dense, rounded GEMM output) -> dG', dU' (dense, zero outside the selected channels).
@@ -717,14 +748,35 @@ __global__ void transpose_kernel(const T* __restrict__ in, int64_t ld_in, T* __r
 // ------------------------------------------------------------------------------------------
 // launchers
 // ------------------------------------------------------------------------------------------
-int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, int write_s, int16_t* idx,
-                       void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
-  if (tokens == 0) return kOk;
-  const int words = static_cast<int>(mask_words(d_ffn));
-  if (write_s && ldg < static_cast<int64_t>(words) * 32) {
-    set_error("select: in-place S' output needs ldg >= %d", words * 32);
+template <typename T>
+static SelFuseT<T> typed_fuse(const SelectFuse* f) {
+  SelFuseT<T> t;
+  t.u_dense = f ? static_cast<const T*>(f->u_dense) : nullptr;
+  t.u_sel = f ? static_cast<T*>(f->u_sel) : nullptr;
+  t.s_sel = f ? static_cast<T*>(f->s_sel) : nullptr;
+  t.z_sel = f ? static_cast<T*>(f->z_sel) : nullptr;
+  return t;
+}
+
+static int check_fuse(const SelectFuse* fuse, int64_t ldg, int words) {
+  if (!fuse) return kOk;
+  if (!fuse->u_dense || !fuse->u_sel) {
+    set_error("select: the fused forward needs the dense U rows and the u_sel output");
     return kErrInvalidArg;
   }
+  if (ldg < static_cast<int64_t>(words) * 32) {
+    set_error("select: in-place Z' output needs ldg >= %d", words * 32);
+    return kErrInvalidArg;
+  }
+  return kOk;
+}
+
+int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, const SelectFuse* fuse,
+                       int16_t* idx, void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
+  if (tokens == 0) return kOk;
+  const int words = static_cast<int>(mask_words(d_ffn));
+  const int frc = check_fuse(fuse, ldg, words);
+  if (frc != kOk) return frc;
   prof_mark(kProfTopk, stream);
   if (tokens <= 1024) {   // few rows: one CTA per row
     const size_t esz = dtype == kBF16 ? 2 : 4;
@@ -734,15 +786,17 @@ int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
       if (smem > 48 * 1024 &&
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
         return check_last("topk_select smem attribute");
-      kern<<<tokens, kCtaSelThreads, smem, stream>>>(static_cast<__nv_bfloat16*>(g), ldg, d_ffn, k, words, write_s, idx,
+      kern<<<tokens, kCtaSelThreads, smem, stream>>>(static_cast<__nv_bfloat16*>(g), ldg, d_ffn, k, words,
+                                                     typed_fuse<__nv_bfloat16>(fuse), idx,
                                                      static_cast<__nv_bfloat16*>(g_sel), bitmap, rank0);
     } else {
       auto kern = topk_select_cta_kernel<float>;
       if (smem > 48 * 1024 &&
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
         return check_last("topk_select smem attribute");
-      kern<<<tokens, kCtaSelThreads, smem, stream>>>(static_cast<float*>(g), ldg, d_ffn, k, words, write_s, idx,
-                                                     static_cast<float*>(g_sel), bitmap, rank0);
+      kern<<<tokens, kCtaSelThreads, smem, stream>>>(static_cast<float*>(g), ldg, d_ffn, k, words,
+                                                     typed_fuse<float>(fuse), idx, static_cast<float*>(g_sel), bitmap,
+                                                     rank0);
     }
     return check_last("topk_select");
   }
@@ -752,29 +806,28 @@ int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
     const unsigned vblocks = static_cast<unsigned>((tokens + kVecSelWarps - 1) / kVecSelWarps);
     uint16_t* gp = static_cast<uint16_t*>(g);
     uint16_t* gs = static_cast<uint16_t*>(g_sel);
-    topk_select_bf16_vec_kernel<<<vblocks, kVecSelWarps * 32, 0, stream>>>(gp, ldg, tokens, d_ffn, k, words, write_s,
-                                                                         idx, gs, bitmap, rank0);
+    topk_select_bf16_vec_kernel<<<vblocks, kVecSelWarps * 32, 0, stream>>>(
+        gp, ldg, tokens, d_ffn, k, words, typed_fuse<__nv_bfloat16>(fuse), idx, gs, bitmap, rank0);
     return check_last("topk_select");
   }
   const unsigned blocks = static_cast<unsigned>((tokens + kSelWarpsPerCta - 1) / kSelWarpsPerCta);
   if (dtype == kBF16)
     topk_select_kernel<__nv_bfloat16><<<blocks, kSelWarpsPerCta * 32, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k, words, write_s, idx, static_cast<__nv_bfloat16*>(g_sel),
-        bitmap, rank0);
+        static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k, words, typed_fuse<__nv_bfloat16>(fuse), idx,
+        static_cast<__nv_bfloat16*>(g_sel), bitmap, rank0);
   else
     topk_select_kernel<float><<<blocks, kSelWarpsPerCta * 32, 0, stream>>>(
-        static_cast<float*>(g), ldg, tokens, d_ffn, k, words, write_s, idx, static_cast<float*>(g_sel), bitmap, rank0);
+        static_cast<float*>(g), ldg, tokens, d_ffn, k, words, typed_fuse<float>(fuse), idx, static_cast<float*>(g_sel),
+        bitmap, rank0);
   return check_last("topk_select");
 }
 
-int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int write_s, int16_t* idx, void* g_sel,
-                       uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
+int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, const SelectFuse* fuse, int16_t* idx,
+                       void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream) {
   if (tokens == 0) return kOk;
   const int words = static_cast<int>(mask_words(d_ffn));
-  if (write_s && ldg < static_cast<int64_t>(words) * 32) {
-    set_error("select: in-place S' output needs ldg >= %d", words * 32);
-    return kErrInvalidArg;
-  }
+  const int frc = check_fuse(fuse, ldg, words);
+  if (frc != kOk) return frc;
   const int k_eff = (d_ffn / 8) * 2 + min(2, d_ffn % 8);
   const int64_t total = static_cast<int64_t>(tokens) * words;
   const int threads = 128;
@@ -782,11 +835,12 @@ int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
   prof_mark(kProfSel2of8, stream);
   if (dtype == kBF16)
     select_2of8_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k_eff, words, write_s, idx,
+        static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k_eff, words, typed_fuse<__nv_bfloat16>(fuse), idx,
         static_cast<__nv_bfloat16*>(g_sel), bitmap, rank0);
   else
     select_2of8_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<float*>(g), ldg, tokens, d_ffn, k_eff, words,
-                                                              write_s, idx, static_cast<float*>(g_sel), bitmap, rank0);
+                                                              typed_fuse<float>(fuse), idx, static_cast<float*>(g_sel),
+                                                              bitmap, rank0);
   return check_last("select_2of8");
 }
 
@@ -825,30 +879,6 @@ int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void
                                                               static_cast<T*>(dense), ld, k);
   }
   return check_last("expand_z");
-}
-
-int launch_gather_sel(int dtype, const int16_t* idx, const void* u_dense, const void* z_dense, const void* g_sel,
-                      void* u_sel, void* s_sel, void* z_sel, int64_t ld, int tokens, int k, cudaStream_t stream) {
-  if (tokens == 0) return kOk;
-  int rc;
-  if (dtype == kBF16) {
-    using T = __nv_bfloat16;
-    const size_t smem = ld * sizeof(T);
-    if ((rc = row_smem_setup<T>(gather_sel_kernel<T>, smem, "gather_sel")) != kOk) return rc;
-    prof_mark(kProfGatherSel, stream);
-    gather_sel_kernel<T><<<tokens, kRowThreads, smem, stream>>>(
-        idx, static_cast<const T*>(u_dense), static_cast<const T*>(z_dense), static_cast<const T*>(g_sel),
-        static_cast<T*>(u_sel), static_cast<T*>(s_sel), static_cast<T*>(z_sel), ld, k);
-  } else {
-    using T = float;
-    const size_t smem = ld * sizeof(T);
-    if ((rc = row_smem_setup<T>(gather_sel_kernel<T>, smem, "gather_sel")) != kOk) return rc;
-    prof_mark(kProfGatherSel, stream);
-    gather_sel_kernel<T><<<tokens, kRowThreads, smem, stream>>>(
-        idx, static_cast<const T*>(u_dense), static_cast<const T*>(z_dense), static_cast<const T*>(g_sel),
-        static_cast<T*>(u_sel), static_cast<T*>(s_sel), static_cast<T*>(z_sel), ld, k);
-  }
-  return check_last("gather_sel");
 }
 
 int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
