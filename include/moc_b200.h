@@ -204,11 +204,16 @@ int64_t moc_decode_static_max_d_ffn(void);
  * kernel it launches and one when an FFN entry point returns. moc_profile_end copies the
  * kernel-kind tag of each recorded event to tags_out and returns their number; the time
  * between events i and i+1 is the duration of kernel i. Tags: 0 end of call, 1 tcgen05 GEMM,
- * 2 CUDA-core GEMM, 3 Top-K select, 4 2:8 select, 5 expand, 6 transpose, 7-11 decode kernels.
+ * 2 CUDA-core GEMM, 3 Top-K select, 4 2:8 select, 5 expand, 6 transpose, 7-11 decode kernels,
+ * 12 sparse backward.
  * No counterpart in the reference, which times whole passes with CUDA events
  * (benchmarks/training/benchmark_training_latency.py:59-106). */
 int moc_profile_begin(void** events, int capacity);
 int moc_profile_end(int* tags_out, int capacity);
+/* Number of GEMM launches this process has put on the library's side stream so far (the rows of a
+ * product that do not fill half a 256-row tile pair run there beside the main launch); these carry
+ * no profile event. No counterpart in the reference. */
+int64_t moc_side_launch_count(void);
 
 /* Synchronises `stream` and returns MOC_OK, or MOC_ERR_DEVICE_TIMEOUT if a kernel of the
  * last call that used `workspace` recorded a bounded-wait failure in its status area. */

@@ -497,6 +497,7 @@ int moc_profile_begin(void** events, int capacity) {
 }
 
 int moc_profile_end(int* tags_out, int capacity) { return profile_end(tags_out, capacity); }
+int64_t moc_side_launch_count(void) { return side_launch_count(); }
 
 int moc_read_status(const void* workspace, void* stream_) {
   if (!workspace) {

@@ -175,7 +175,7 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
     return check_last("gemm smem attribute");
   const int tiles = sh.tiles_m * sh.tiles_n * sh.groups;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  prof_mark(kProfGemmTc, stream);
+  if (!p.no_prof) prof_mark(kProfGemmTc, stream);
   kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(maps, sh, epi);
   return check_last("gemm_tcgen05");
 }
@@ -232,7 +232,7 @@ static int launch_tcgen05_pair(const GemmProblem& p, const Epi& epi, cudaStream_
   }
   const int tiles = sh.tiles_m * sh.tiles_n * sh.groups;
   const int pairs = tiles < max_clusters ? tiles : max_clusters;
-  prof_mark(kProfGemmTc, stream);
+  if (!p.no_prof) prof_mark(kProfGemmTc, stream);
   kern<<<2 * pairs, kGemmThreads, kPairSmemBytes, stream>>>(maps, sh, epi);
   return check_last("gemm_tcgen05_pair");
 }
@@ -333,6 +333,64 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
   }
 }
 
+static int launch_gemm_whole(const GemmProblem& p, cudaStream_t stream) {
+  if (p.dtype == kBF16) return dispatch_epilogue<__nv_bfloat16>(p, stream);
+  if (p.dtype == kF32) return dispatch_epilogue<float>(p, stream);
+  set_error("unsupported dtype %d", p.dtype);
+  return kErrInvalidArg;
+}
+
+// ---- M-tail split ------------------------------------------------------------------------------------
+// The CTA-pair kernel works in 256-row tiles on sm_count / 2 clusters with a static schedule, so a launch takes
+// ceil(tiles / clusters) rounds. When the last rows of M fill at most half a tile pair and cutting them off saves
+// a whole round, they run as 128-row tiles of the single-CTA kernel on a side stream instead, on the SMs whose
+// clusters have no tile in the last round (the weight-gradient GEMM of the 1b preset: 528 pair tiles = 8 rounds,
+// against 504 = 7 rounds plus 24 single-CTA tiles on the 28 SMs that idle in the 7th).
+struct SideLane {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ok = false;
+};
+static std::mutex g_side_mutex;
+static int64_t g_side_launches = 0;   // guarded by g_side_mutex
+int64_t side_launch_count() {
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  return g_side_launches;
+}
+
+// One side stream and event pair per device, created at the first split launch on that device (a call that
+// should not be the first one inside a stream capture).
+static SideLane* side_lane() {
+  static SideLane lanes[64];
+  static bool tried[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!tried[dev]) {
+    tried[dev] = true;
+    SideLane& l = lanes[dev];
+    l.ok = cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming) == cudaSuccess;
+    if (!l.ok) cudaGetLastError();
+  }
+  return lanes[dev].ok ? &lanes[dev] : nullptr;
+}
+
+static bool tail_split_rows(const GemmProblem& p, int* m_main) {
+  if (p.dtype != kBF16 || p.impl != 0 || p.epi.kind != kEpiStore || !pair_kernel_enabled() || !p.status) return false;
+  const int pair_rows = 2 * kBlockM;
+  const int tail = p.m % pair_rows;
+  if (tail == 0 || tail > kBlockM || p.m < 2 * pair_rows) return false;
+  const int clusters = sm_count() / 2;
+  const int per_row = ceil_div_i(p.n, kBlockN) * p.groups;
+  const int main_tiles = (p.m / pair_rows) * per_row;
+  const int rounds_main = ceil_div_i(main_tiles, clusters);
+  if (rounds_main >= ceil_div_i(main_tiles + per_row, clusters)) return false;   // no round saved
+  if (per_row > 2 * (rounds_main * clusters - main_tiles)) return false;          // tail would not fit the idle SMs
+  *m_main = p.m - tail;
+  return true;
+}
+
 int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
   if (p.m <= 0 || p.n <= 0) return kOk;
   if (p.groups < 1 || p.groups > kGemmMaxGroups || (p.groups > 1 && p.k1 > 0)) {
@@ -343,10 +401,38 @@ int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
     set_error("GEMM needs K >= 1 and non-null operands");
     return kErrInvalidArg;
   }
-  if (p.dtype == kBF16) return dispatch_epilogue<__nv_bfloat16>(p, stream);
-  if (p.dtype == kF32) return dispatch_epilogue<float>(p, stream);
-  set_error("unsupported dtype %d", p.dtype);
-  return kErrInvalidArg;
+  int m_main = 0;
+  SideLane* lane = nullptr;
+  if (!tail_split_rows(p, &m_main) || !(lane = side_lane())) return launch_gemm_whole(p, stream);
+
+  GemmProblem head = p, tail = p;
+  head.m = m_main;
+  head.impl = 2;
+  tail.m = p.m - m_main;
+  tail.impl = 3;
+  tail.no_prof = 1;
+  const int nops = p.k1 > 0 ? 2 : p.groups;
+  for (int i = 0; i < nops; ++i) {
+    const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(p.a[i].ptr);
+    tail.a[i].ptr = a + (p.a[i].mn_major ? static_cast<int64_t>(m_main) : static_cast<int64_t>(m_main) * p.a[i].ld);
+  }
+  for (int g = 0; g < p.groups; ++g) {
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.epi.c[g]);
+    if (c) tail.epi.c[g] = c + (p.epi.transposed[g] ? static_cast<int64_t>(m_main) : static_cast<int64_t>(m_main) * p.epi.ldc[g]);
+  }
+  // the fork / join sequence is enqueued under a lock: the lane's events are shared by all host threads
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  if (cudaEventRecord(lane->fork, stream) != cudaSuccess ||
+      cudaStreamWaitEvent(lane->stream, lane->fork, 0) != cudaSuccess)
+    return check_last("GEMM tail fork");
+  int rc = launch_gemm_whole(head, stream);
+  const int rc_tail = launch_gemm_whole(tail, lane->stream);
+  if (rc_tail == kOk) ++g_side_launches;
+  // join even after a failed launch so that the side stream never stays attached to a capture
+  if (cudaEventRecord(lane->join, lane->stream) != cudaSuccess ||
+      cudaStreamWaitEvent(stream, lane->join, 0) != cudaSuccess)
+    return check_last("GEMM tail join");
+  return rc != kOk ? rc : rc_tail;
 }
 
 }  // namespace moc

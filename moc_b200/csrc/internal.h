@@ -35,7 +35,9 @@ struct EpiArgs {
 // C = A_0[m, k0] * B_0[n, k0]^T + A_1[m, k1] * B_1[n, k1]^T.
 struct GemmProblem {
   int dtype;                 // DType
-  int impl;                  // 0: default for the dtype (bf16 -> tcgen05, f32 -> SIMT); 1: force SIMT
+  int impl;                  // 0: default for the dtype (bf16 -> tcgen05, f32 -> SIMT); 1: force SIMT;
+                             // 2 / 3: force the CTA-pair / single-CTA tcgen05 kernel
+  int no_prof;               // 1: the launch records no profile event (used for side-stream launches)
   int m, n;
   int groups;                // 1..3 same-shape problems in one launch
   int k0;
@@ -46,6 +48,8 @@ struct GemmProblem {
 };
 
 int launch_gemm(const GemmProblem& p, cudaStream_t stream);
+// GEMM launches put on the side stream so far (tail rows of M, see launch_gemm)
+int64_t side_launch_count();
 
 // ---- selection / auxiliary kernels (kernels.cu) ---------------------------------------------
 // Optional forward fusion of a selection launch: with `fuse` set the kernel also gathers u = U[t, ch] of every

@@ -57,6 +57,7 @@ CASES = [
     (3, 5461, 2048),     # odd N (d_ffn of the 1b preset), tiny M
     (640, 384, 5461),    # odd K
     (1000, 777, 1200),   # several 256-row tile pairs with a tail in each dimension
+    (4693, 1024, 192),   # 18 tile pairs + 85 rows on 148 SMs: impl 0 runs the tail rows as a second kernel on a side stream
 ]
 
 # bf16 tensor-core cores: 0 = automatic choice, 2 = CTA-pair kernel (256-row tiles), 3 = single-CTA kernel
@@ -72,7 +73,7 @@ def test_tcgen05_gemm_bf16(impl, m, n, k, a_mn, b_mn):
     torch.testing.assert_close(got, ref.bfloat16().float(), rtol=2 ** -7, atol=1e-2 * max(1.0, (k / 64) ** 0.5))
 
 
-@pytest.mark.parametrize("m,n,k", [(130, 300, 100), (256, 512, 320)])
+@pytest.mark.parametrize("m,n,k", [(130, 300, 100), (256, 512, 320), (4693, 1024, 192)])
 @pytest.mark.parametrize("impl", TC_IMPLS)
 def test_tcgen05_gemm_transposed_store(impl, m, n, k):
     got, ref = _run_gemm(torch.bfloat16, impl, m, n, k, 1, 1, 1, seed=7)
