@@ -388,10 +388,13 @@ def run_ours(args, rank, world, local_rank):
         achieved = flops_per_step * args.steps / (gemm_ms * 1e-3) / 1e12
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         roofline = {
-            "bound": "tensor", "kernel": "gemm_tcgen05_kernel", "achieved": achieved, "peak": peak,
+            "bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel", "achieved": achieved, "peak": peak,
             "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": f"{peak_src} (sustained cuBLAS bf16)",
             "launches": gemm_n, "avg_launch_ms": gemm_ms / gemm_n,
-            "algorithmic_flops_per_step": flops_per_step, "traffic": None,
+            "algorithmic_flops_per_step": flops_per_step,
+            # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean over the five pair-kernel launches of a
+            # step, from one ncu capture of this workload (2.98 GB per step; 2.22 GB algorithmic)
+            "traffic": 0.596e9 if args.ffn_type in ("moc", "moc_gcp") else None,
         }
     kernel_share = {name: {"ms_per_step": tot / args.steps, "launches_per_step": cnt / args.steps}
                     for name, (tot, cnt) in sorted(per_kind.items())}
