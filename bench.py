@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
     ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--overlap", type=int, default=1, help="N>1: 1 = start the gradient all-reduce beside the dX GEMM")
+    ap.add_argument("--reserve-sms", type=int, default=16, help="N>1 with --overlap: SMs the dX GEMM leaves free")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N>1: cap on the CTAs of an NCCL kernel (0: NCCL default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode FFN micro-benchmark (N=1 only)")
     return ap.parse_args()
@@ -61,7 +64,9 @@ def workload_config(args, world):
                     f"X[8,2048,{D}] bf16, ffn_type={args.ffn_type}",
         "tokens_per_gpu": args.tokens,
         "global_tokens": args.tokens * world,
-        "parallelism": f"token-sharded dp{world}" if world > 1 else "single GPU",
+        "parallelism": (f"token-sharded dp{world}, one NCCL all-reduce of the three weight gradients per step"
+                        + (f", started beside the dX GEMM ({args.reserve_sms} SMs reserved)" if args.overlap else
+                           ", after the backward pass")) if world > 1 else "single GPU",
         "l2": "inputs larger than L2: every step streams >600 MB of activations, weights and scratch "
               "(126 MB L2), no explicit flush",
     }
@@ -287,6 +292,8 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        if args.nccl_max_ctas > 0:
+            os.environ["NCCL_MAX_CTAS"] = str(args.nccl_max_ctas)
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.lib()   # raises if the CUDA library is missing
 
@@ -302,7 +309,8 @@ def run_ours(args, rank, world, local_rank):
     dy_host = torch.randn(8, tokens // 8, D, generator=gx).bfloat16().pin_memory()
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
-    reducer = GradAllReducer(average=True) if world > 1 else None
+    reducer = (GradAllReducer(average=True, overlap=bool(args.overlap), reserve_sms=args.reserve_sms)
+               if world > 1 else None)
 
     def step(xin, dyin):
         module.zero_grad(set_to_none=True)

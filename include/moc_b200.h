@@ -214,6 +214,10 @@ int moc_profile_end(int* tags_out, int capacity);
  * product that do not fill half a 256-row tile pair run there beside the main launch); these carry
  * no profile event. No counterpart in the reference. */
 int64_t moc_side_launch_count(void);
+/* Data-parallel training: the dX GEMM, the last kernel of moc_ffn_bwd, leaves `sms` SMs (0..64, default 0) free
+ * so that a gradient all-reduce started behind the weight-gradient events of moc_ffn_bwd runs beside it.
+ * Process-wide. No counterpart in the reference (it has no distributed code). */
+int moc_set_overlap_sm_reserve(int sms);
 
 /* Synchronises `stream` and returns MOC_OK, or MOC_ERR_DEVICE_TIMEOUT if a kernel of the
  * last call that used `workspace` recorded a bounded-wait failure in its status area. */

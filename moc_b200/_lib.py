@@ -39,6 +39,7 @@ SIGNATURES = {
     "moc_profile_begin": (c_int, [_P, c_int]),
     "moc_profile_end": (c_int, [_P, c_int]),
     "moc_side_launch_count": (c_int64, []),
+    "moc_set_overlap_sm_reserve": (c_int, [c_int]),
     "moc_read_status": (c_int, [_P, _P]),
     "moc_dense_ffn_fwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 8 + [c_int64, _P]),
     "moc_dense_ffn_bwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 12 + [c_int64, _P]),

@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/moc_b200.h"
 #include "common.cuh"
 #include "internal.h"
@@ -17,6 +19,11 @@ using namespace moc;
 namespace {
 
 constexpr int64_t kStatusBytes = 256;
+// The status area holds 64 ints, zeroed at the start of every FFN call: [0] the time-out word of the bounded
+// device waits, [16..] one tile counter per GEMM launch of the call (CTA-pair kernel, tiles in arrival order).
+constexpr int kTileCounterFirst = 16;
+// SMs that the dX GEMM of a backward call leaves free (moc_set_overlap_sm_reserve)
+std::atomic<int> g_overlap_sm_reserve{0};
 
 inline size_t esize(int dtype) { return dtype == kBF16 ? 2 : 4; }
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
@@ -198,6 +205,7 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   p.epi.ldc[0] = ld;
   p.epi.c[1] = u_dense;
   p.epi.ldc[1] = ld;
+  p.tile_counter = status + kTileCounterFirst;
   if ((rc = launch_gemm(p, stream)) != kOk) return rc;
 
   // channel selection on the rounded G (moc/ffn.py:144-147); the same kernel gathers the selected channels of U
@@ -216,6 +224,7 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   q.a[0] = operand(dense, ld, 0);
   q.b[0] = operand(w_down_t, d, 1);
   q.epi = store_epi(y, d, 0);
+  q.tile_counter = status + kTileCounterFirst + 1;
   rc = launch_gemm(q, stream);
   prof_mark(kProfEnd, stream);
   return rc;
@@ -272,6 +281,7 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   z.a[0] = operand(grad_y, d, 0);
   z.b[0] = operand(w_down_t, d, 0);
   z.epi = store_epi(buf_u, ld, 0);
+  z.tile_counter = status + kTileCounterFirst;
   if ((rc = launch_gemm(z, stream)) != kOk) return rc;
 
   // gather through the mask, SiLU', zero fill -> dense dG', dU' (moc/ffn.py:209-237)
@@ -299,6 +309,7 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   w.epi.ldc[1] = d;
   w.epi.c[2] = grad_w_up;
   w.epi.ldc[2] = d;
+  w.tile_counter = status + kTileCounterFirst + 1;
   if ((rc = launch_gemm(w, stream)) != kOk) return rc;
   if ((rc = record(ev_down, stream)) != kOk || (rc = record(ev_gate, stream)) != kOk ||
       (rc = record(ev_up, stream)) != kOk)
@@ -312,6 +323,8 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   gx.a[1] = operand(buf_u, ld, 0);
   gx.b[1] = operand(w_up, d, 1);
   gx.epi = store_epi(grad_x, d, 0);
+  gx.tile_counter = status + kTileCounterFirst + 2;
+  gx.sm_reserve = g_overlap_sm_reserve.load(std::memory_order_relaxed);   // room for the gradient all-reduce
   rc = launch_gemm(gx, stream);
   prof_mark(kProfEnd, stream);
   return rc;
@@ -356,6 +369,7 @@ int moc_dense_ffn_fwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
   q.a[0] = operand(z, ld, 0);
   q.b[0] = operand(w_down_t, d, 1);
   q.epi = store_epi(y, d, 0);
+  q.tile_counter = status + kTileCounterFirst + 1;
   rc = launch_gemm(q, stream);
   prof_mark(kProfEnd, stream);
   return rc;
@@ -398,6 +412,7 @@ int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
   z.a[0] = operand(grad_y, d, 0);
   z.b[0] = operand(w_down_t, d, 0);
   z.epi = store_epi(buf_u, ld, 0);
+  z.tile_counter = status + kTileCounterFirst;
   if ((rc = launch_gemm(z, stream)) != kOk) return rc;
   // (padding columns [d_ffn, ld) of the dense matrices hold unspecified values; no GEMM reads them)
   if ((rc = launch_dense_bwd(dtype, g, u, buf_u, buf_z, buf_g, tokens * ld, stream)) != kOk) return rc;
@@ -418,6 +433,7 @@ int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
   w.epi.ldc[1] = d;
   w.epi.c[2] = grad_w_up;
   w.epi.ldc[2] = d;
+  w.tile_counter = status + kTileCounterFirst + 1;
   if ((rc = launch_gemm(w, stream)) != kOk) return rc;
   GemmProblem gx = problem(dtype, status, tokens, d, d_ffn);
   gx.k1 = (int)d_ffn;
@@ -426,6 +442,8 @@ int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
   gx.a[1] = operand(buf_u, ld, 0);
   gx.b[1] = operand(w_up, d, 1);
   gx.epi = store_epi(grad_x, d, 0);
+  gx.tile_counter = status + kTileCounterFirst + 2;
+  gx.sm_reserve = g_overlap_sm_reserve.load(std::memory_order_relaxed);   // room for the gradient all-reduce
   rc = launch_gemm(gx, stream);
   prof_mark(kProfEnd, stream);
   return rc;
@@ -498,6 +516,15 @@ int moc_profile_begin(void** events, int capacity) {
 
 int moc_profile_end(int* tags_out, int capacity) { return profile_end(tags_out, capacity); }
 int64_t moc_side_launch_count(void) { return side_launch_count(); }
+
+int moc_set_overlap_sm_reserve(int sms) {
+  if (sms < 0 || sms > 64) {
+    set_error("moc_set_overlap_sm_reserve: %d is outside 0..64", sms);
+    return kErrInvalidArg;
+  }
+  g_overlap_sm_reserve.store(sms, std::memory_order_relaxed);
+  return kOk;
+}
 
 int moc_read_status(const void* workspace, void* stream_) {
   if (!workspace) {

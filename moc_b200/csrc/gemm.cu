@@ -170,6 +170,7 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
   sh.tiles_m = ceil_div_i(p.m, kBlockM);
   sh.tiles_n = ceil_div_i(p.n, kBlockN);
   sh.status = p.status;
+  sh.tile_counter = nullptr;
   auto kern = gemm_tcgen05_kernel<Epi>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) != cudaSuccess)
     return check_last("gemm smem attribute");
@@ -207,6 +208,7 @@ static int launch_tcgen05_pair(const GemmProblem& p, const Epi& epi, cudaStream_
   sh.tiles_m = ceil_div_i(p.m, 2 * kBlockM);   // 256-row tile pairs
   sh.tiles_n = ceil_div_i(p.n, kBlockN);
   sh.status = p.status;
+  sh.tile_counter = p.tile_counter;
   auto kern = gemm_tcgen05_pair_kernel<Epi>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
     return check_last("gemm pair smem attribute");
@@ -231,7 +233,9 @@ static int launch_tcgen05_pair(const GemmProblem& p, const Epi& epi, cudaStream_
     max_clusters = n;
   }
   const int tiles = sh.tiles_m * sh.tiles_n * sh.groups;
-  const int pairs = tiles < max_clusters ? tiles : max_clusters;
+  int avail = max_clusters - (p.sm_reserve + 1) / 2;
+  if (avail < 1) avail = 1;
+  const int pairs = tiles < avail ? tiles : avail;
   if (!p.no_prof) prof_mark(kProfGemmTc, stream);
   kern<<<2 * pairs, kGemmThreads, kPairSmemBytes, stream>>>(maps, sh, epi);
   return check_last("gemm_tcgen05_pair");
@@ -377,7 +381,9 @@ static SideLane* side_lane() {
 }
 
 static bool tail_split_rows(const GemmProblem& p, int* m_main) {
-  if (p.dtype != kBF16 || p.impl != 0 || p.epi.kind != kEpiStore || !pair_kernel_enabled() || !p.status) return false;
+  if (p.dtype != kBF16 || p.impl != 0 || p.epi.kind != kEpiStore || !pair_kernel_enabled() || !p.status ||
+      p.sm_reserve > 0)
+    return false;
   const int pair_rows = 2 * kBlockM;
   const int tail = p.m % pair_rows;
   if (tail == 0 || tail > kBlockM || p.m < 2 * pair_rows) return false;

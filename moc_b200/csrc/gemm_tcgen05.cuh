@@ -60,6 +60,7 @@ struct GemmShape {
   int a_mn, b_mn;    // 1 = operand is MN-major in memory
   int tiles_m, tiles_n;
   int* status;       // device status word
+  int* tile_counter; // pair kernel only: zeroed device int; tiles are handed out in arrival order (null: round-robin)
 };
 
 template <class Epi>

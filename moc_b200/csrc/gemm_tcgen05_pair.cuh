@@ -13,6 +13,13 @@
 //   empty[s]   (both)        <- tcgen05.commit multicast by the leader's MMA thread
 //   tfull[a]   (both)        <- tcgen05.commit multicast after the last k-block of a tile
 //   tempty[a]  (leader)      <- one arrive per epilogue warp of both CTAs (remote for the peer)
+//   sfull[q]   (both)        <- the leader's producer thread after it wrote tile index q of the tile queue
+//   sempty[q]  (leader)      <- every consumer of a queue slot: MMA thread, peer producer, all epilogue warps
+// Tile queue: the leader's producer thread decides the next tile of the pair - round-robin over the clusters, or,
+// when the launch passes a zeroed device counter, by atomicAdd in arrival order, so that clusters that start
+// late or lose their SMs to another kernel (a collective on a side stream) simply take fewer tiles - and
+// publishes it to a small ring in the shared memory of both CTAs. The fetch of tile i+1 is issued before the
+// loads of tile i, so its latency is hidden. A tile index >= num_tiles ends every role.
 // Every wait is bounded; an abort is recorded in the status word and makes all roles of the CTA leave.
 #pragma once
 
@@ -30,6 +37,8 @@ constexpr int kPairTileABytes = kBlockM * kBlockK * 2;          // 128 rows of A
 constexpr int kPairTileBBytes = (kBlockN / 2) * kBlockK * 2;    // 128 of the 256 rows of B: 16 KiB
 constexpr int kPairStageBytes = kPairTileABytes + kPairTileBBytes;
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr int kSchedDepth = 4;   // producer runs at most one tile ahead of the MMAs, the epilogue at most two behind
+constexpr uint32_t kSchedConsumers = 2 * kEpiWarps + 2;   // epilogue warps of both CTAs, MMA thread, peer producer
 
 template <class Epi>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
@@ -41,8 +50,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
   uint64_t* empty_bar = bars + kPairStages;       // [kPairStages]
   uint64_t* tfull_bar = bars + 2 * kPairStages;   // [2]
   uint64_t* tempty_bar = tfull_bar + 2;           // [2] used in the leader CTA only
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* sfull_bar = tempty_bar + 2;           // [kSchedDepth]
+  uint64_t* sempty_bar = sfull_bar + kSchedDepth; // [kSchedDepth] used in the leader CTA only
+  uint32_t* sched_tile = reinterpret_cast<uint32_t*>(sempty_bar + kSchedDepth);   // [kSchedDepth]
+  uint32_t* tmem_slot = sched_tile + kSchedDepth;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  static_assert((2 * kPairStages + 4 + 2 * kSchedDepth) * 8 + kSchedDepth * 4 + 8 <= 256, "barrier area overflow");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -69,6 +82,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
     ptx::mbar_init(&tfull_bar[1], 1);
     ptx::mbar_init(&tempty_bar[0], 2 * kEpiWarps);
     ptx::mbar_init(&tempty_bar[1], 2 * kEpiWarps);
+#pragma unroll
+    for (int q = 0; q < kSchedDepth; ++q) {
+      ptx::mbar_init(&sfull_bar[q], 1);
+      ptx::mbar_init(&sempty_bar[q], kSchedConsumers);
+    }
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async_smem();
@@ -84,11 +102,43 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    // ------------------------------ TMA producer (both CTAs); the leader's also feeds the tile queue ------
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      uint32_t cur = 0;
+      if (rank == 0)
+        cur = sh.tile_counter ? static_cast<uint32_t>(atomicAdd(sh.tile_counter, 1)) : static_cast<uint32_t>(pair);
+      for (uint32_t qi = 0; ok; ++qi) {
+        const int q = qi % kSchedDepth;
+        const uint32_t qph = (qi / kSchedDepth) & 1u;
+        uint32_t nxt = 0;
+        if (rank == 0) {
+          // next tile first: the atomic's round trip overlaps the loads of the current tile
+          if (cur < static_cast<uint32_t>(num_tiles))
+            nxt = sh.tile_counter ? static_cast<uint32_t>(atomicAdd(sh.tile_counter, 1)) : cur + num_pairs;
+          else
+            nxt = cur;
+          if (!ptx::mbar_wait_cluster(&sempty_bar[q], qph ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(sh.status, 0, (kDevTimeoutProducer << 24) | 0x800000 | (qi & 0x7FFFFF));
+            break;
+          }
+          sched_tile[q] = cur;
+          ptx::st_shared_cluster_u32(ptx::map_to_cta(ptx::smem_u32(&sched_tile[q]), 1), cur);
+          ptx::mbar_arrive(&sfull_bar[q]);
+          ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&sfull_bar[q]), 1));
+        } else {
+          if (!ptx::mbar_wait_cluster(&sfull_bar[q], qph, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(sh.status, 0, (kDevTimeoutProducer << 24) | 0x400000 | (qi & 0x3FFFFF));
+            break;
+          }
+          cur = sched_tile[q];
+          ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&sempty_bar[q]), 0));
+        }
+        if (cur >= static_cast<uint32_t>(num_tiles)) break;
+        const int tile = static_cast<int>(cur);
         const int group = tile / tiles_per_group;
         const int t = tile - group * tiles_per_group;
         const int m0 = (t / sh.tiles_n) * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
@@ -98,7 +148,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
           const uint32_t ph = (it / kPairStages) & 1u;
           if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
             *abort_flag = 1;
-            atomicCAS(sh.status, 0, (kDevTimeoutProducer << 24) | (it & 0xFFFFFF));
+            atomicCAS(sh.status, 0, (kDevTimeoutProducer << 24) | (it & 0x3FFFFF));
             ok = false;
             break;
           }
@@ -126,6 +176,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
               ptx::tma_load_2d_pair(sb + i * kMnBoxBytes, tb, full_leader, n0 + 64 * i, kk);
           }
         }
+        cur = nxt;
       }
     }
     __syncwarp();
@@ -137,10 +188,21 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
       const uint32_t b_lbo = sh.b_mn ? kMnBoxBytes : 0, b_step = sh.b_mn ? kUmmaK * 128 : kUmmaK * 2;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
+      for (; ok; ++tcount) {
+        {
+          const int q = tcount % kSchedDepth;
+          if (!ptx::mbar_wait(&sfull_bar[q], (tcount / kSchedDepth) & 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(sh.status, 0, (kDevTimeoutMma << 24) | 0xC00000 | (tcount & 0x3FFFFF));
+            break;
+          }
+          const uint32_t tile = sched_tile[q];
+          ptx::mbar_arrive(&sempty_bar[q]);
+          if (tile >= static_cast<uint32_t>(num_tiles)) break;
+        }
         const uint32_t acc = tcount & 1u;
         const uint32_t aph = (tcount >> 1) & 1u;
-        if (!ptx::mbar_wait(&tempty_bar[acc], aph ^ 1u, abort_flag)) {
+        if (!ptx::mbar_wait_cluster(&tempty_bar[acc], aph ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(sh.status, 0, (kDevTimeoutMma << 24) | 0x800000 | (tcount & 0x7FFFFF));
           break;
@@ -178,8 +240,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
     constexpr int kChunks = kEpiPartCols / 32;
     const uint32_t tempty_leader0 = ptx::map_to_cta(ptx::smem_u32(&tempty_bar[0]), 0);
     const uint32_t tempty_leader1 = ptx::map_to_cta(ptx::smem_u32(&tempty_bar[1]), 0);
-    uint32_t tcount = 0;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++tcount) {
+    const uint32_t sempty_leader = ptx::map_to_cta(ptx::smem_u32(&sempty_bar[0]), 0);
+    for (uint32_t tcount = 0;; ++tcount) {
+      const int q = tcount % kSchedDepth;
+      if (!ptx::mbar_wait_cluster(&sfull_bar[q], (tcount / kSchedDepth) & 1u, abort_flag)) {
+        *abort_flag = 1;
+        atomicCAS(sh.status, 0, (kDevTimeoutEpilogue << 24) | 0x800000 | (tcount & 0x7FFFFF));
+        break;
+      }
+      const int tile = static_cast<int>(sched_tile[q]);
+      __syncwarp();   // every lane has read the slot before it is handed back
+      if (lane == 0) ptx::mbar_arrive_cluster(sempty_leader + q * 8);
+      if (tile >= num_tiles) break;
       const uint32_t acc = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
       const int group = tile / tiles_per_group;
@@ -193,7 +265,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmShape 
       if (active) epi.begin(ctx, group, row, col_first, nchunks);
       if (!ptx::mbar_wait(&tfull_bar[acc], aph, abort_flag)) {
         *abort_flag = 1;
-        atomicCAS(sh.status, 0, (kDevTimeoutEpilogue << 24) | (tcount & 0xFFFFFF));
+        atomicCAS(sh.status, 0, (kDevTimeoutEpilogue << 24) | (tcount & 0x7FFFFF));
         break;
       }
       ptx::tc_fence_after_sync();

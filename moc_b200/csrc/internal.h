@@ -38,6 +38,9 @@ struct GemmProblem {
   int impl;                  // 0: default for the dtype (bf16 -> tcgen05, f32 -> SIMT); 1: force SIMT;
                              // 2 / 3: force the CTA-pair / single-CTA tcgen05 kernel
   int no_prof;               // 1: the launch records no profile event (used for side-stream launches)
+  int* tile_counter;         // CTA-pair kernel: zeroed device int -> tiles are handed out in arrival order
+                             // (null: round-robin over the clusters)
+  int sm_reserve;            // CTA-pair kernel: SMs left free for a kernel that runs beside this launch
   int m, n;
   int groups;                // 1..3 same-shape problems in one launch
   int k0;

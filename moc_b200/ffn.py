@@ -92,9 +92,12 @@ def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, idx, g_sel, u_sel, s
     code = _lib.dtype_code(dt)
     dev = x2d.device
     dx = torch.empty(tokens, d, device=dev, dtype=dt)
-    d_gate = torch.empty(d_ffn, d, device=dev, dtype=dt)
-    d_up = torch.empty(d_ffn, d, device=dev, dtype=dt)
-    d_down = torch.empty(d, d_ffn, device=dev, dtype=dt)
+    # the three weight gradients are views of one buffer, so that a data-parallel caller can reduce them with a
+    # single collective (moc_b200.dp)
+    bucket = torch.empty(3, d_ffn * d, device=dev, dtype=dt)
+    d_down = bucket[0].view(d, d_ffn)
+    d_gate = bucket[1].view(d_ffn, d)
+    d_up = bucket[2].view(d_ffn, d)
     ws_bytes = lib.moc_ffn_bwd_workspace_bytes(code, tokens, d_ffn)
     ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
     evs = [None, None, None]
@@ -107,7 +110,7 @@ def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, idx, g_sel, u_sel, s
                          _lib.stream_ptr(dev))
     _lib.check(rc, "moc_ffn_bwd")
     _maybe_check_status(ws, dev)
-    return dx, d_gate, d_up, d_down
+    return dx, d_gate, d_up, d_down, bucket
 
 
 _CHECK_STATUS = False
@@ -129,14 +132,16 @@ def _maybe_check_status(ws: torch.Tensor, dev) -> None:
 # autograd
 # ------------------------------------------------------------------------------------------
 
-# Hook for data-parallel training: when set, it is called as hook(name, grad, event) for
-# name in ("down", "gate", "up") right after the backward kernels were enqueued; `event` is
-# recorded on the compute stream at the point where `grad` is final. See moc_b200.dp.
+# Hook for data-parallel training: when set, it is called right after the backward kernels were enqueued, as
+# hook("bucket", flat, event) with the [3, d_ffn * d] buffer that the three returned weight gradients are views
+# of (down, gate, up), or, when a parameter dtype differs from the compute dtype, as hook(name, grad, event) for
+# name in ("down", "gate", "up"). `event` is recorded on the compute stream at the point where the gradient is
+# final. The hook may reduce the tensor in place. See moc_b200.dp.
 _grad_ready_hook = None
 # True: events fire as soon as the weight-gradient GEMM is done, so a reduction can run beside the dX GEMM.
-# False (default): one event after the whole backward pass. Measured on 2 x B200: a collective running beside
-# the persistent, statically scheduled dX GEMM delays some of its CTAs and doubles its duration (0.55 -> 1.04 ms),
-# far more than the 0.15 ms the all-reduce of the three gradients takes on NVLink when it runs alone.
+# False (default): one event after the whole backward pass. The dX GEMM hands out its tiles in arrival order, so a
+# collective that takes SMs away only makes it proportionally slower; for the collective to find free SMs while
+# the GEMM runs, the caller also reserves some (moc_set_overlap_sm_reserve, see moc_b200.dp.GradAllReducer).
 _grad_ready_early = False
 
 
@@ -200,8 +205,9 @@ class _MoCB200Function(torch.autograd.Function):
             events = tuple(torch.cuda.Event() for _ in range(3))
             for ev in events:
                 ev.record()   # PyTorch creates the CUDA event lazily; the library re-records it
-        dx, d_gate, d_up, d_down = moc_ffn_backward(go, x2d, gw, uw, down_w_t, idx, g_sel, u_sel, s_sel,
-                                                    z_sel, events)
+        dx, d_gate, d_up, d_down, bucket = moc_ffn_backward(go, x2d, gw, uw, down_w_t, idx, g_sel, u_sel, s_sel,
+                                                            z_sel, events)
+        same_dtype = all(dt == bucket.dtype for dt in ctx.w_dtypes)
         d_gate = d_gate.to(ctx.w_dtypes[0])
         d_up = d_up.to(ctx.w_dtypes[1])
         d_down = d_down.to(ctx.w_dtypes[2])
@@ -209,7 +215,9 @@ class _MoCB200Function(torch.autograd.Function):
             done = torch.cuda.Event()
             done.record()          # after the last backward kernel
             events = (done, done, done)
-        if hook is not None:
+        if hook is not None and same_dtype:
+            hook("bucket", bucket, events[2])      # one collective over the three gradients (views of `bucket`)
+        elif hook is not None:
             hook("down", d_down, events[0])
             hook("gate", d_gate, events[1])
             hook("up", d_up, events[2])
