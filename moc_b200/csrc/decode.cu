@@ -18,6 +18,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "internal.h"
@@ -297,6 +298,8 @@ struct DecodeWs {
   uint32_t* bitmap;  // [batch, words]
   uint16_t* rank0;   // [batch, words]
   float* partial;    // [splits, batch, d]
+  int* hist;         // single-launch path: [min(batch, 8), 2048]
+  uint16_t* seg;     // single-launch path: compact (channel, z) segments of the CTAs
   int64_t bytes;
 };
 
@@ -317,6 +320,8 @@ static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
     return r;
   };
   w.status = reinterpret_cast<int*>(take(256));
+  // directly behind the status area: one memset clears both before a single-launch call
+  w.hist = reinterpret_cast<int*>(take(decode_fused_hist_bytes(batch < 8 ? batch : 8)));
   w.gate = reinterpret_cast<bf16*>(take(batch * ld * 2));
   w.u = reinterpret_cast<bf16*>(take(batch * ld * 2));
   w.idx = reinterpret_cast<int16_t*>(take(batch * d_ffn * 2));
@@ -325,6 +330,7 @@ static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
   w.bitmap = reinterpret_cast<uint32_t*>(take(batch * words * 4));
   w.rank0 = reinterpret_cast<uint16_t*>(take(batch * words * 2));
   w.partial = reinterpret_cast<float*>(take(partial_bound(batch, d, d_ffn)));
+  w.seg = reinterpret_cast<uint16_t*>(take(decode_fused_seg_words(batch < 8 ? batch : 8, d_ffn) * 2));
   w.bytes = p - static_cast<uint8_t*>(base);
   return w;
 }
@@ -442,6 +448,28 @@ static int check_decode_args(const char* who, int64_t batch, int64_t d, int64_t 
   return kOk;
 }
 
+// MOC_B200_DECODE_FUSED=0 in the environment keeps small batches on the multi-kernel path (a switch for A/B timing).
+static bool fused_decode_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MOC_B200_DECODE_FUSED");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// The single launch wins at batch 1 (measured at the 1b shape, inside CUDA graphs: 27 against 30 us for the Top-K
+// rule, 22 against 29 us for 2:8); from batch 2 on its per-row work in shared memory makes the multi-kernel path
+// faster. MOC_B200_DECODE_FUSED_MAX_BATCH (1..8) overrides the limit for experiments.
+static int64_t fused_decode_max_batch() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MOC_B200_DECODE_FUSED_MAX_BATCH");
+    v = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 1;
+  }
+  return v;
+}
+
 int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, const void* x, const void* gate_scores,
                   const void* w_gate, const void* w_up, const void* w_down_t, void* y, void* workspace,
                   int64_t workspace_bytes, cudaStream_t stream) {
@@ -449,6 +477,13 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
   if (rc != kOk) return rc;
   if (batch == 0) return kOk;
   const DecodeWs w = carve(workspace, batch, d, d_ffn);
+  if (fused_decode_enabled() && batch <= fused_decode_max_batch() && decode_fused_supported(batch, d, d_ffn)) {
+    // very small batches: the whole FFN in one cooperative launch
+    rc = launch_decode_fused(rule, (int)batch, (int)d, (int)d_ffn, (int)k, x, gate_scores, d_ffn, w_gate, w_up,
+                             w_down_t, y, w.gate, w.seg, ffn_ld(d_ffn), w.hist, w.status, stream);
+    prof_mark(kProfEnd, stream);
+    return rc;
+  }
   if (batch >= kDecodeGemmMinBatch && cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess)
     return check_last("cudaMemsetAsync");
   const bf16* xb = static_cast<const bf16*>(x);

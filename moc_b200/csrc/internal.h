@@ -89,12 +89,22 @@ int launch_transpose(int dtype, const void* in, int64_t ld_in, void* out, int64_
 enum ProfTag : int {
   kProfEnd = 0, kProfGemmTc = 1, kProfGemmSimt = 2, kProfTopk = 3, kProfSel2of8 = 4, kProfExpand = 5,
   kProfTranspose = 6, kProfDecodeGate = 7, kProfDecodeUp = 8, kProfDecodeDown = 9, kProfDecodeFused28 = 10,
-  kProfDecodeDense = 11, kProfBwdSparse = 12,
+  kProfDecodeDense = 11, kProfBwdSparse = 12, kProfDecodeFused = 13,
 };
 void prof_mark(int tag, cudaStream_t stream);
 
 // ---- decode path (decode.cu), bf16 only ---------------------------------------------------------
 int64_t decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn);
+// Single-launch decode for batches of up to 8 rows (decode_fused.cu). g_scratch: [batch, ld] bf16; seg_scratch:
+// decode_fused_seg_words(batch, d_ffn) 16-bit words; hist: decode_fused_hist_bytes(batch) bytes; status_area:
+// 64 ints ([0] status word, [32] barrier counter).
+bool decode_fused_supported(int64_t batch, int64_t d, int64_t d_ffn);
+int64_t decode_fused_hist_bytes(int64_t batch);
+int64_t decode_fused_seg_words(int64_t batch, int64_t d_ffn);
+int launch_decode_fused(int rule, int batch, int d, int d_ffn, int k, const void* x, const void* scores,
+                        int64_t ld_scores, const void* w_gate, const void* w_up, const void* w_down_t, void* y,
+                        void* g_scratch, void* seg_scratch, int64_t ld, int* hist, int* status_area,
+                        cudaStream_t stream);
 // rule 0: global Top-K, 1: 2-of-8. gate_scores != null: use the caller's [batch, d_ffn] scores instead of x * W_gate^T
 int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, const void* x, const void* gate_scores,
                   const void* w_gate, const void* w_up, const void* w_down_t, void* y, void* workspace,
