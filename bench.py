@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the MoC sparse SwiGLU FFN hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ffn-type moc|moc_gcp|moc_2_8]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ffn-type moc|moc_gcp|moc_2_8|dense]
 
 Workload (N = 1 and every rank of N > 1): one MoC FFN layer at the 1b-preset shape
 (d=2048, d_ffn=5461, K=1024), bf16, X [8, 2048, 2048] = 16 384 tokens per GPU, forward +
@@ -46,7 +46,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8"])
+    ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8", "dense"],
+                    help="dense = the dense SwiGLU comparison row of the same shape")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
     ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
     ap.add_argument("--no-e2e", action="store_true")
@@ -86,6 +87,9 @@ def cpu_oracle_step_fn(ffn_type):
     select = "2of8" if ffn_type == "moc_2_8" else "topk"
 
     def step():
+        if ffn_type == "dense":
+            O.dense_forward_backward(x, wg, wu, wd, dy)
+            return
         fwd = O.moc_forward(x, wg, wu, wd, K_SEL, select=select)
         if ffn_type == "moc_gcp":
             O.moc_backward(dy, x, wg, wu, wd, fwd["idx"], fwd["g_sel"], fwd["u_sel"])

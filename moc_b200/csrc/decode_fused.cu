@@ -101,29 +101,6 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
   return s_ok != 0;
 }
 
-// exclusive scan of one value per thread over the CTA in thread order; total in every thread
-__device__ __forceinline__ uint32_t fused_exscan(uint32_t v, uint32_t* wsum, uint32_t& total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t inc = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t nb = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-    if (lane >= o) inc += nb;
-  }
-  if (lane == 31) wsum[warp] = inc;
-  __syncthreads();
-  uint32_t woff = 0, tot = 0;
-#pragma unroll
-  for (int i = 0; i < kFusedWarps; ++i) {
-    const uint32_t s = wsum[i];
-    if (i < warp) woff += s;
-    tot += s;
-  }
-  total = tot;
-  __syncthreads();
-  return woff + inc - v;
-}
-
 #ifdef MOC_FUSED_TIMING
 __device__ unsigned long long g_fused_t[8 * 512];
 #define FUSED_STAMP(i)                                                         \

@@ -552,6 +552,140 @@ topk_select_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, i
   }
 }
 
+// bf16 fast path of the 2:8 rule: one warp per token row, and one 16-byte vector = one group of 8 channels
+// per lane and step, so the gate row, the dense U row and the Z' row move as coalesced vectors and the compact
+// outputs of a group land at the fixed position 2 * group. Needs rows padded to the mask width and 16-byte
+// aligned; same outputs as select_2of8_kernel.
+constexpr int kVec28Warps = 4;
+
+__global__ void __launch_bounds__(kVec28Warps * 32)
+select_2of8_bf16_vec_kernel(uint16_t* __restrict__ g, int64_t ldg, int tokens, int d_ffn, int k_eff, int words,
+                            SelFuseT<__nv_bfloat16> fuse, int16_t* __restrict__ idx, uint16_t* __restrict__ g_sel,
+                            uint32_t* __restrict__ bitmap, uint16_t* __restrict__ rank0) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kVec28Warps + warp;
+  if (row >= tokens) return;
+  uint4* grow4 = reinterpret_cast<uint4*>(g + static_cast<int64_t>(row) * ldg);
+  const uint4* urow4 = reinterpret_cast<const uint4*>(fuse.u_dense + static_cast<int64_t>(row) * ldg);
+  const int64_t crow = static_cast<int64_t>(row) * k_eff;
+  int16_t* idx_row = idx + crow;
+  uint16_t* gsel_row = g_sel + crow;
+  uint16_t* usel_row = reinterpret_cast<uint16_t*>(fuse.u_sel) + crow;
+  uint16_t* ssel_row = fuse.s_sel ? reinterpret_cast<uint16_t*>(fuse.s_sel) + crow : nullptr;
+  uint16_t* zsel_row = fuse.z_sel ? reinterpret_cast<uint16_t*>(fuse.z_sel) + crow : nullptr;
+  uint32_t* bm_row = bitmap + static_cast<int64_t>(row) * words;
+  uint16_t* rk_row = rank0 + static_cast<int64_t>(row) * words;
+  const int nvec = words * 4;
+  const int nslots = (nvec + 31) >> 5;
+  // even k_eff and 4-byte aligned arrays: every group's pair of compact entries starts on a 4-byte boundary
+  const bool pair_stores = (k_eff & 1) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(idx) | reinterpret_cast<uintptr_t>(g_sel) |
+                             reinterpret_cast<uintptr_t>(fuse.u_sel) | reinterpret_cast<uintptr_t>(fuse.s_sel) |
+                             reinterpret_cast<uintptr_t>(fuse.z_sel)) & 3u) == 0;
+  // the vectors of the next step are requested before the current ones are worked on
+  uint4 q_next = make_uint4(0u, 0u, 0u, 0u), uq_next = make_uint4(0u, 0u, 0u, 0u);
+  if (lane < nvec) {
+    q_next = grow4[lane];
+    if (fuse.u_dense) uq_next = urow4[lane];
+  }
+#pragma unroll 1
+  for (int i = 0; i < nslots; ++i) {
+    const int v = i * 32 + lane;
+    uint4 q = q_next, uq = uq_next;
+    if (v + 32 < nvec) {
+      q_next = grow4[v + 32];
+      if (fuse.u_dense) uq_next = urow4[v + 32];
+    }
+    const int nv = min(8, max(0, d_ffn - 8 * v));
+    const uint32_t gw[4] = {q.x, q.y, q.z, q.w}, uw[4] = {uq.x, uq.y, uq.z, uq.w};
+    uint32_t bits[8], key[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      bits[j] = (gw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+      key[j] = j < nv ? order_key16(static_cast<uint16_t>(bits[j])) : 0u;
+    }
+    int b1 = 0;
+#pragma unroll
+    for (int j = 1; j < 8; ++j)
+      if (j < nv && key[j] > key[b1]) b1 = j;     // first maximum: the lower channel wins ties
+    int b2 = -1;
+    uint32_t k2 = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool cand = j < nv && j != b1 && (b2 < 0 || key[j] > k2);
+      if (cand) {
+        b2 = j;
+        k2 = key[j];
+      }
+    }
+    const int lo = (b2 >= 0 && b2 < b1) ? b2 : b1;
+    const int hi = (b2 >= 0 && b2 < b1) ? b1 : b2;
+    uint32_t g_lo = 0, g_hi = 0, u_lo = 0, u_hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {   // constant-index register reads only
+      const uint32_t ub = (uw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+      if (j == lo) { g_lo = bits[j]; u_lo = ub; }
+      if (j == hi) { g_hi = bits[j]; u_hi = ub; }
+    }
+    uint32_t m8 = 0;
+    if (nv > 0) {
+      const int pos = 2 * v;
+      m8 = 1u << lo;
+      if (hi >= 0) m8 |= 1u << hi;
+      if (hi >= 0 && pair_stores) {   // both entries of the group in one 4-byte store
+        *reinterpret_cast<uint32_t*>(idx_row + pos) = static_cast<uint32_t>(8 * v + lo) | (static_cast<uint32_t>(8 * v + hi) << 16);
+        *reinterpret_cast<uint32_t*>(gsel_row + pos) = g_lo | (g_hi << 16);
+      } else {
+        idx_row[pos] = static_cast<int16_t>(8 * v + lo);
+        gsel_row[pos] = static_cast<uint16_t>(g_lo);
+        if (hi >= 0) {
+          idx_row[pos + 1] = static_cast<int16_t>(8 * v + hi);
+          gsel_row[pos + 1] = static_cast<uint16_t>(g_hi);
+        }
+      }
+      if (fuse.u_dense) {
+        float s0, z0, s1 = 0.0f, z1 = 0.0f;
+        moc_fwd_point<__nv_bfloat16>(__uint_as_float(g_lo << 16), __uint_as_float(u_lo << 16), s0, z0);
+        if (hi >= 0) moc_fwd_point<__nv_bfloat16>(__uint_as_float(g_hi << 16), __uint_as_float(u_hi << 16), s1, z1);
+        const uint32_t zb0 = __float_as_uint(z0) >> 16, zb1 = __float_as_uint(z1) >> 16;   // already bf16 values
+        const uint32_t sb0 = __float_as_uint(s0) >> 16, sb1 = __float_as_uint(s1) >> 16;
+        if (hi >= 0 && pair_stores) {
+          *reinterpret_cast<uint32_t*>(usel_row + pos) = u_lo | (u_hi << 16);
+          if (ssel_row) *reinterpret_cast<uint32_t*>(ssel_row + pos) = sb0 | (sb1 << 16);
+          if (zsel_row) *reinterpret_cast<uint32_t*>(zsel_row + pos) = zb0 | (zb1 << 16);
+        } else {
+          usel_row[pos] = static_cast<uint16_t>(u_lo);
+          if (ssel_row) ssel_row[pos] = static_cast<uint16_t>(sb0);
+          if (zsel_row) zsel_row[pos] = static_cast<uint16_t>(zb0);
+          if (hi >= 0) {
+            usel_row[pos + 1] = static_cast<uint16_t>(u_hi);
+            if (ssel_row) ssel_row[pos + 1] = static_cast<uint16_t>(sb1);
+            if (zsel_row) zsel_row[pos + 1] = static_cast<uint16_t>(zb1);
+          }
+        }
+        uint32_t zw[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t zj = (j == lo) ? zb0 : ((j == hi) ? zb1 : 0u);
+          zw[j >> 1] |= zj << (16 * (j & 1));
+        }
+        q = make_uint4(zw[0], zw[1], zw[2], zw[3]);
+      }
+    } else if (fuse.u_dense) {
+      q = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (fuse.u_dense && v < nvec) grow4[v] = q;    // Z' over the whole padded row
+    uint32_t b = m8 << (8 * (lane & 3));
+    b |= __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+    b |= __shfl_xor_sync(0xFFFFFFFFu, b, 2);
+    const int widx = i * 8 + (lane >> 2);
+    if ((lane & 3) == 0 && widx < words) {
+      bm_row[widx] = b;
+      rk_row[widx] = static_cast<uint16_t>(min(widx * 8, k_eff));
+    }
+  }
+}
+
 // One thread per (token, 32-channel word) = 4 groups of 8. Lower channel index wins ties
 // (moc/inference/triton_fused_ffn_kernels.py:103-114). fuse: as in topk_select_kernel.
 template <typename T>
@@ -833,6 +967,15 @@ int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, c
   const int threads = 128;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   prof_mark(kProfSel2of8, stream);
+  if (dtype == kBF16 && ldg >= static_cast<int64_t>(words) * 32 && ldg % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(g) & 15u) == 0 &&
+      (!fuse || (reinterpret_cast<uintptr_t>(fuse->u_dense) & 15u) == 0)) {
+    const unsigned vblocks = static_cast<unsigned>((tokens + kVec28Warps - 1) / kVec28Warps);
+    select_2of8_bf16_vec_kernel<<<vblocks, kVec28Warps * 32, 0, stream>>>(
+        static_cast<uint16_t*>(g), ldg, tokens, d_ffn, k_eff, words, typed_fuse<__nv_bfloat16>(fuse), idx,
+        static_cast<uint16_t*>(g_sel), bitmap, rank0);
+    return check_last("select_2of8");
+  }
   if (dtype == kBF16)
     select_2of8_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
         static_cast<__nv_bfloat16*>(g), ldg, tokens, d_ffn, k_eff, words, typed_fuse<__nv_bfloat16>(fuse), idx,

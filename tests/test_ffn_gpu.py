@@ -254,3 +254,39 @@ def test_materialized_saved_set_matches_oracle():
     out = m(xs)
     out.backward(grad_y.cuda())
     assert torch.isfinite(xs.grad.float()).all()
+
+
+def test_sm_reserve_and_bucketed_gradients():
+    """moc_set_overlap_sm_reserve only changes how many clusters the dX GEMM uses: every gradient keeps its bits.
+    The three weight gradients of one backward pass are views of one [3, d_ffn * d] buffer (down, gate, up), the
+    layout the data-parallel reducer relies on for its single collective."""
+    from moc_b200 import _lib
+    tokens, d, d_ffn, k = 1024, 512, 1376, 256
+    x, grad_y, wg, wu, wd = O.make_inputs(tokens, d, d_ffn, torch.bfloat16, seed=77)
+    base = _run_gpu("moc", x, grad_y, wg, wu, wd, k)
+    lib = _lib.lib()
+    assert lib.moc_set_overlap_sm_reserve(65) < 0 and "outside" in _lib.last_error()
+    seen = {}
+
+    def hook(name, grad, event):
+        seen[name] = grad
+
+    _lib.check(lib.moc_set_overlap_sm_reserve(16), "reserve")
+    moc_b200.set_grad_ready_hook(hook, early=True)
+    try:
+        m = _module("moc", d, d_ffn, k, torch.bfloat16, wg, wu, wd)
+        xs = x.cuda().requires_grad_(True)
+        m(xs).backward(grad_y.cuda())
+        torch.cuda.synchronize()
+    finally:
+        moc_b200.set_grad_ready_hook(None)
+        lib.moc_set_overlap_sm_reserve(0)
+    assert torch.equal(xs.grad.cpu(), base["dx"])
+    assert torch.equal(m.gate_proj.weight.grad.cpu(), base["d_gate_w"])
+    assert torch.equal(m.down_proj.weight.grad.cpu(), base["d_down_w"])
+    assert list(seen) == ["bucket"] and seen["bucket"].shape == (3, d_ffn * d)
+    b = seen["bucket"]
+    assert torch.equal(b[0].view(d, d_ffn), m.down_proj.weight.grad)
+    assert torch.equal(b[1].view(d_ffn, d), m.gate_proj.weight.grad)
+    assert torch.equal(b[2].view(d_ffn, d), m.up_proj.weight.grad)
+    assert b.data_ptr() == m.down_proj.weight.grad.data_ptr()      # views, not copies

@@ -96,6 +96,10 @@ def test_select_2of8(dtype, tokens, d_ffn):
     _check(g, None, rule="2of8")
     gi = torch.randint(-1, 2, (tokens, d_ffn), generator=torch.Generator().manual_seed(1)).to(dtype)
     _check(gi, None, rule="2of8")
+    # rows padded to the mask width (NaN in the padding): the bf16 vector kernel, one group of 8 per 16-byte load
+    ld = _lib.lib().moc_ffn_ld(d_ffn)
+    _check(g, None, ld=ld, rule="2of8")
+    _check(gi, None, ld=ld, rule="2of8")
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
