@@ -12,6 +12,10 @@
 //                            (selected_down_*_tile_kernel, optimized_global_moc_ext.cu:247-372; split-K as
 //                            in moc/inference/triton_fused_ffn_kernels.py:315-370 but without atomics)
 //   decode_reduce_kernel   : y[b, :] = round(sum over s of partial[s, b, :]), fixed summation order
+//   skinny_consume_kernel  : batches of 16 rows and more: the three projections run as skinny split-K products on
+//                            the tcgen05 core (one 128-row tile and K range per SM, each weight matrix streamed
+//                            once); this kernel reduces the up (and gate) partial blocks, applies SiLU, the product
+//                            and the selection bitmap and writes the dense zero-filled Z' that the down product reads
 //
 // Rounding points follow the dense masking reference (inference_ffn.py:169-180) with bf16 tensors:
 // gate scores, U, s = SiLU(g), z = s * u and y are each rounded to bf16 once.
@@ -167,14 +171,73 @@ __global__ void decode_z_from_u_kernel(const bf16* __restrict__ u, int64_t ld_u,
   z[i] = __float2bfloat16_rn(s * bf16_load(u + static_cast<int64_t>(b) * ld_u + idx[i]));
 }
 
-// z[b, f] = round(round(SiLU(g[b, f])) * u[b, f]) over dense rows (dense baseline for larger batches)
-__global__ void decode_swiglu_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, int64_t ld,
-                                     bf16* __restrict__ z, int batch, int d_ffn) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<int64_t>(batch) * d_ffn) return;
-  const int b = static_cast<int>(i / d_ffn), f = static_cast<int>(i - static_cast<int64_t>(b) * d_ffn);
-  const float s = silu_round<bf16>(bf16_load(g + b * ld + f));
-  z[i] = __float2bfloat16_rn(s * bf16_load(u + b * ld + f));
+// Consumers of the split-K partial blocks of a skinny product (element [i][b] of block s at (s * rows + i) * ldp
+// + b, i = weight row, b = batch row). Both read the blocks along b (coalesced), turn 32 x 32 tiles in shared
+// memory and write bf16 rows out[b, i] along i (coalesced).
+//   MODE 0: out[b, i] = round(sum_s P[s][i][b])                                   (gate scores, y)
+//   MODE 1: Z'[b, f] = mask ? round(round(SiLU(g)) * round(sum_s U[s][f][b])) : 0 for f < ld (zero beyond d_ffn);
+//           g from bf16 score rows, or round(sum_s G[s][f][b]) for the dense baseline; bitmap null: every channel.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+skinny_consume_kernel(const float* __restrict__ p0, const float* __restrict__ p1, int splits, int rows, int batch,
+                      int64_t ldp, bf16* __restrict__ out, int64_t ld_out, int out_cols, const bf16* __restrict__ g_rows,
+                      int64_t ld_g, const uint32_t* __restrict__ bitmap, int words) {
+  __shared__ float tile0[32][33];
+  __shared__ float tile1[MODE == 1 ? 32 : 1][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  const int i0 = blockIdx.x * 32, b0 = blockIdx.y * 32;
+  const int64_t block = static_cast<int64_t>(rows) * ldp;
+  {
+    // the four rows of a thread are loaded together for every split: independent loads, one round trip per split
+    float v0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, v1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int b = b0 + tx;
+    for (int sidx = 0; sidx < splits; ++sidx) {
+      float t0[4], t1[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = i0 + ty + 8 * k;
+        const bool ok = i < rows && b < batch;
+        const int64_t at = sidx * block + static_cast<int64_t>(ok ? i : 0) * ldp + (ok ? b : 0);
+        t0[k] = ok ? __ldcs(p0 + at) : 0.0f;
+        t1[k] = (MODE == 1 && p1 && ok) ? __ldcs(p1 + at) : 0.0f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v0[k] += t0[k];
+        v1[k] += t1[k];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      tile0[ty + 8 * k][tx] = v0[k];
+      if (MODE == 1) tile1[ty + 8 * k][tx] = v1[k];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 32; k += 8) {
+    const int b = b0 + ty + k, i = i0 + tx;
+    if (b >= batch || i >= out_cols) continue;
+    float r = 0.0f;
+    if (MODE == 0) {
+      r = tile0[tx][ty + k];
+    } else if (i < rows && (!bitmap || ((bitmap[static_cast<int64_t>(b) * words + (i >> 5)] >> (i & 31)) & 1u))) {
+      const float u = bf16_round(tile0[tx][ty + k]);
+      const float g = p1 ? bf16_round(tile1[tx][ty + k]) : bf16_load(g_rows + static_cast<int64_t>(b) * ld_g + i);
+      r = silu_round<bf16>(g) * u;
+    }
+    out[static_cast<int64_t>(b) * ld_out + i] = __float2bfloat16_rn(r);
+  }
+}
+
+template <int MODE>
+static int launch_skinny_consume(const float* p0, const float* p1, int splits, int rows, int batch, bf16* out,
+                                 int64_t ld_out, int out_cols, const bf16* g_rows, int64_t ld_g,
+                                 const uint32_t* bitmap, int words, cudaStream_t stream) {
+  const dim3 grid(ceil_div_i(out_cols, 32), ceil_div_i(batch, 32));
+  skinny_consume_kernel<MODE><<<grid, 256, 0, stream>>>(p0, p1, splits, rows, batch, round_up_i64(batch, 4), out, ld_out,
+                                                       out_cols, g_rows, ld_g, bitmap, words);
+  return check_last("skinny_consume");
 }
 
 constexpr int kDownMaxRows = 256;
@@ -303,11 +366,24 @@ struct DecodeWs {
   int64_t bytes;
 };
 
+// measured at the 1b shape: the skinny tensor-core products win from 16 rows for the MoC paths (56 against 59 us at
+// 8 rows) and from 8 rows for the dense baseline (47 against 68 us)
+constexpr int kDecodeGemmMinBatch = 16;
+constexpr int kDenseGemmMinBatch = 8;
+
+// fp32 bytes of the split-K partial blocks of one skinny product: splits * tiles of 128 rows <= SM count
+static int64_t splitk_partial_bytes(int64_t batch) {
+  return (static_cast<int64_t>(device_sms()) + 2) * 128 * round_up_i64(batch, 4) * 4;
+}
+
 static int64_t partial_bound(int64_t batch, int64_t d, int64_t d_ffn) {
   // plan_down: splits <= target / (batch * dchunks) + 2, or ceil(k / kDownMaxRows) when the slice cap binds
   const int64_t by_target = static_cast<int64_t>(device_sms()) * 3 / 2 + 2 * batch + 8;
   const int64_t by_cap = batch * ((d_ffn + kDownMaxRows - 1) / kDownMaxRows + 1);
-  return (by_target > by_cap ? by_target : by_cap) * d * 4;
+  const int64_t gather = (by_target > by_cap ? by_target : by_cap) * d * 4;
+  // batches that go through the split-K GEMMs keep two partial sets (gate and up of the dense baseline)
+  const int64_t skinny = batch >= kDenseGemmMinBatch ? 2 * round_up_i64(splitk_partial_bytes(batch), 256) : 0;
+  return gather > skinny ? gather : skinny;
 }
 
 static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
@@ -363,32 +439,63 @@ static int launch_gemv(const bf16* x, const bf16* w, const bf16* w2, bf16* out, 
   return check_last("decode_gemv");
 }
 
-// out[b, f] = round(x[b, :] . W[f, :]) for every row of W. Batches of 16 rows and more go through the tcgen05
-// GEMM core as out^T[F, batch] = W * x^T with a transposed store (43 tiles at the 1b shape, each streaming
-// 128 weight rows once); smaller batches use the CUDA-core GEMV.
-constexpr int kDecodeGemmMinBatch = 16;
+// Skinny product on the tensor cores for batches of 16 rows and more: P[s][i][b] = partial sums over the s-th range
+// of K of A[i, :] . Bt[b, :], with A the weight matrix ([rows, K] K-major, or [K, rows] when a_mn) and Bt the
+// [batch, K] activations. The single-CTA tcgen05 kernel runs rows / 128 tiles x `splits` K ranges so that about
+// one tile per SM streams the weights once; the caller reduces the partial blocks (launch_splitk_reduce or a
+// consumer kernel). ldp = round_up(batch, 4) floats per partial row.
+static int skinny_splits(int rows, int k) {
+  const int tiles = ceil_div_i(rows, 128);
+  const int kb = ceil_div_i(k, 64);
+  int splits = device_sms() / tiles;
+  if (splits < 1) splits = 1;
+  if (splits > kb) splits = kb;
+  while (splits > 1 && ceil_div_i(kb, splits) * (splits - 1) >= kb) --splits;   // every range gets a k-block
+  return splits;
+}
 
-static int project_rows(const bf16* x, const bf16* w, bf16* out, int64_t ld_out, int batch, int d, int rows,
-                        int* status, cudaStream_t stream) {
-  if (batch < kDecodeGemmMinBatch) return launch_gemv<false>(x, w, nullptr, out, ld_out, batch, d, rows, stream);
+static int skinny_gemm(const bf16* a, int64_t lda, int a_mn, const bf16* bt, int64_t ldb, int rows, int batch, int k,
+                       float* partial, int* splits_out, int* status, cudaStream_t stream) {
   GemmProblem p = {};
   p.dtype = kBF16;
   p.status = status;
   p.m = rows;
   p.n = batch;
-  p.k0 = d;
+  p.k0 = k;
   p.groups = 1;
-  p.a[0].ptr = w;
-  p.a[0].ld = d;
-  p.a[0].mn_major = 0;
-  p.b[0].ptr = x;
-  p.b[0].ld = d;
+  p.k_splits = skinny_splits(rows, k);
+  p.a[0].ptr = a;
+  p.a[0].ld = lda;
+  p.a[0].mn_major = a_mn;
+  p.b[0].ptr = bt;
+  p.b[0].ld = ldb;
   p.b[0].mn_major = 0;
-  p.epi.kind = kEpiStore;
-  p.epi.c[0] = out;
-  p.epi.ldc[0] = ld_out;
-  p.epi.transposed[0] = 1;
+  p.epi.kind = kEpiPartialF32;
+  p.epi.partial = partial;
+  p.epi.ld_partial = round_up_i64(batch, 4);
+  *splits_out = p.k_splits;
   return launch_gemm(p, stream);
+}
+
+// out[b, f] = round(x[b, :] . W[f, :]) for every row of W: CUDA-core GEMV for small batches, split-K tensor-core
+// product plus reduction for batches of 16 rows and more.
+static int project_rows(const bf16* x, const bf16* w, bf16* out, int64_t ld_out, int batch, int d, int rows,
+                        int* status, float* partial, cudaStream_t stream) {
+  if (batch < kDecodeGemmMinBatch) return launch_gemv<false>(x, w, nullptr, out, ld_out, batch, d, rows, stream);
+  int splits = 1;
+  int rc = skinny_gemm(w, d, 0, x, d, rows, batch, d, partial, &splits, status, stream);
+  if (rc != kOk) return rc;
+  return launch_skinny_consume<0>(partial, nullptr, splits, rows, batch, out, ld_out, rows, nullptr, 0, nullptr, 0, stream);
+}
+
+// y[b, :] = round(sum over f of Z'[b, f] * W_down^T[f, :]) from dense zero-filled Z' rows (leading dimension ld)
+static int down_dense(const bf16* z_dense, int64_t ld, const bf16* w_down_t, bf16* y, int batch, int d, int d_ffn,
+                      int* status, float* partial, cudaStream_t stream) {
+  int splits = 1;
+  prof_mark(kProfDecodeDown, stream);
+  int rc = skinny_gemm(w_down_t, d, 1, z_dense, ld, d, batch, d_ffn, partial, &splits, status, stream);
+  if (rc != kOk) return rc;
+  return launch_skinny_consume<0>(partial, nullptr, splits, d, batch, y, d, d, nullptr, 0, nullptr, 0, stream);
 }
 
 static int launch_down(const bf16* z, const int16_t* idx, const bf16* w_down_t, bf16* y, float* partial, int batch,
@@ -410,13 +517,26 @@ static int launch_down(const bf16* z, const int16_t* idx, const bf16* w_down_t, 
 }
 
 // after the channel set is known: z for the selected channels, then the gathered down projection
-static int selected_tail(const DecodeWs& w, const bf16* x, const bf16* w_up, const bf16* w_down_t, bf16* y, int batch,
-                         int d, int d_ffn, int k, cudaStream_t stream) {
+static int selected_tail(const DecodeWs& w, const bf16* x, const bf16* scores, int64_t ld_scores, const bf16* w_up,
+                         const bf16* w_down_t, bf16* y, int batch, int d, int d_ffn, int k, cudaStream_t stream) {
   int rc;
   const int64_t total = static_cast<int64_t>(batch) * k;
+  if (total > d_ffn && batch >= kDecodeGemmMinBatch) {
+    // Larger batches select (nearly) every row of W_up and W_down between them: three skinny tensor-core
+    // products that stream each weight matrix once, with the mask applied to a dense zero-filled Z'.
+    const int64_t ld = ffn_ld(d_ffn);
+    int splits = 1;
+    float* up_partial = w.partial;
+    prof_mark(kProfDecodeUp, stream);
+    if ((rc = skinny_gemm(w_up, d, 0, x, d, d_ffn, batch, d, up_partial, &splits, w.status, stream)) != kOk) return rc;
+    if ((rc = launch_skinny_consume<1>(up_partial, nullptr, splits, d_ffn, batch, w.u, ld, static_cast<int>(ld), scores,
+                                       ld_scores, w.bitmap, static_cast<int>(mask_words(d_ffn)), stream)) != kOk)
+      return rc;
+    return down_dense(w.u, ld, w_down_t, y, batch, d, d_ffn, w.status, w.partial, stream);
+  }
   if (total > d_ffn) {
     // the batch selects more rows than W_up has: one dense pass over W_up, then pick
-    if ((rc = project_rows(x, w_up, w.u, ffn_ld(d_ffn), batch, d, d_ffn, w.status, stream)) != kOk) return rc;
+    if ((rc = project_rows(x, w_up, w.u, ffn_ld(d_ffn), batch, d, d_ffn, w.status, w.partial, stream)) != kOk) return rc;
     prof_mark(kProfDecodeUp, stream);
     decode_z_from_u_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(w.u, ffn_ld(d_ffn), w.g_sel,
                                                                                          w.idx, w.z, batch, k);
@@ -493,7 +613,7 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
     scores = const_cast<void*>(gate_scores);
     ld_scores = d_ffn;
   } else if ((rc = project_rows(xb, static_cast<const bf16*>(w_gate), w.gate, ld_scores, (int)batch, (int)d,
-                                (int)d_ffn, w.status, stream)) != kOk) {
+                                (int)d_ffn, w.status, w.partial, stream)) != kOk) {
     return rc;
   }
   if (rule == 0)
@@ -503,8 +623,9 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
     rc = launch_select_2of8(kBF16, scores, ld_scores, (int)batch, (int)d_ffn, nullptr, w.idx, w.g_sel, w.bitmap, w.rank0,
                             stream);
   if (rc != kOk) return rc;
-  rc = selected_tail(w, xb, static_cast<const bf16*>(w_up), static_cast<const bf16*>(w_down_t),
-                     static_cast<bf16*>(y), (int)batch, (int)d, (int)d_ffn, (int)k, stream);
+  rc = selected_tail(w, xb, static_cast<const bf16*>(scores), ld_scores, static_cast<const bf16*>(w_up),
+                     static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), (int)batch, (int)d, (int)d_ffn, (int)k,
+                     stream);
   prof_mark(kProfEnd, stream);
   return rc;
 }
@@ -515,20 +636,30 @@ int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const v
   if (rc != kOk) return rc;
   if (batch == 0) return kOk;
   const DecodeWs w = carve(workspace, batch, d, d_ffn);
-  // z[b, f] = SiLU(g) * u for every channel, stored with row stride d_ffn so that it reads as a compact z
-  if (batch >= kDecodeGemmMinBatch) {
+  if (batch >= kDenseGemmMinBatch) {
+    // three skinny tensor-core products; SwiGLU is applied while the gate and up partial blocks are reduced
     if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
     const int64_t ld = ffn_ld(d_ffn);
-    if ((rc = project_rows(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate), w.gate, ld, (int)batch,
-                           (int)d, (int)d_ffn, w.status, stream)) != kOk ||
-        (rc = project_rows(static_cast<const bf16*>(x), static_cast<const bf16*>(w_up), w.u, ld, (int)batch, (int)d,
-                           (int)d_ffn, w.status, stream)) != kOk)
+    const bf16* xb = static_cast<const bf16*>(x);
+    float* g_partial = w.partial;
+    float* u_partial = w.partial + round_up_i64(splitk_partial_bytes(batch), 256) / 4;
+    int splits = 1, splits_u = 1;
+    prof_mark(kProfDecodeDense, stream);
+    if ((rc = skinny_gemm(static_cast<const bf16*>(w_gate), d, 0, xb, d, (int)d_ffn, (int)batch, (int)d, g_partial,
+                          &splits, w.status, stream)) != kOk ||
+        (rc = skinny_gemm(static_cast<const bf16*>(w_up), d, 0, xb, d, (int)d_ffn, (int)batch, (int)d, u_partial,
+                          &splits_u, w.status, stream)) != kOk)
       return rc;
-    const int64_t total = batch * d_ffn;
-    decode_swiglu_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(w.gate, w.u, ld, w.z,
-                                                                                        (int)batch, (int)d_ffn);
-    if ((rc = check_last("decode_swiglu")) != kOk) return rc;
-  } else if ((rc = launch_gemv<true>(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate),
+    if ((rc = launch_skinny_consume<1>(u_partial, g_partial, splits, (int)d_ffn, (int)batch, w.u, ld, static_cast<int>(ld),
+                                       nullptr, 0, nullptr, 0, stream)) != kOk)
+      return rc;
+    rc = down_dense(w.u, ld, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), (int)batch, (int)d, (int)d_ffn,
+                    w.status, w.partial, stream);
+    prof_mark(kProfEnd, stream);
+    return rc;
+  }
+  // z[b, f] = SiLU(g) * u for every channel, stored with row stride d_ffn so that it reads as a compact z
+  if ((rc = launch_gemv<true>(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate),
                                      static_cast<const bf16*>(w_up), w.z, d_ffn, (int)batch, (int)d, (int)d_ffn,
                                      stream)) != kOk) {
     return rc;

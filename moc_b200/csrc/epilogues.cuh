@@ -133,6 +133,33 @@ struct EpiStore {
   }
 };
 
+// ---- split-K partial results: fp32 accumulator rows, one [m, ld] block per (group, split) -----------
+// A reduction kernel adds the blocks of a group in a fixed order and rounds once (splitk_reduce_kernel).
+template <typename T>
+struct EpiPartialF32 {
+  struct Ctx {};
+  float* p;               // [groups * splits][m][ld]
+  int64_t ld;             // floats per row, a multiple of 4
+  int64_t block_stride;   // m * ld
+  int n;
+
+  __device__ __forceinline__ void begin(Ctx&, int, int, int, int) const {}
+  __device__ __forceinline__ void prefetch(Ctx&, int, int, int) const {}
+  __device__ __forceinline__ void operator()(Ctx&, int group, int row, int col0, int, const float (&acc)[32]) const {
+    float* dst = p + group * block_stride + static_cast<int64_t>(row) * ld + col0;
+    const int ncols = min(32, n - col0);
+    if (ncols == 32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) dst[j] = acc[j];
+    }
+  }
+};
+
 // ---- dense SwiGLU forward: acc = U tile, Z = round(round(SiLU(G)) * round(U)) ------------
 // (moc/ffn.py:120-121). Reads G, writes U (kept for the backward pass) and Z.
 template <typename T>

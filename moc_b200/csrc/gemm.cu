@@ -171,10 +171,16 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
   sh.tiles_n = ceil_div_i(p.n, kBlockN);
   sh.status = p.status;
   sh.tile_counter = nullptr;
+  sh.k_splits = p.k_splits > 1 ? p.k_splits : 1;
+  if (sh.k_splits > 1 && (p.k1 > 0 || sh.k_splits > sh.kb0 ||
+                          ceil_div_i(sh.kb0, sh.k_splits) * (sh.k_splits - 1) >= sh.kb0)) {
+    set_error("split-K needs a single K segment and at least one k-block per split");
+    return kErrInvalidArg;
+  }
   auto kern = gemm_tcgen05_kernel<Epi>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes) != cudaSuccess)
     return check_last("gemm smem attribute");
-  const int tiles = sh.tiles_m * sh.tiles_n * sh.groups;
+  const int tiles = sh.tiles_m * sh.tiles_n * sh.groups * sh.k_splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   if (!p.no_prof) prof_mark(kProfGemmTc, stream);
   kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(maps, sh, epi);
@@ -209,6 +215,7 @@ static int launch_tcgen05_pair(const GemmProblem& p, const Epi& epi, cudaStream_
   sh.tiles_n = ceil_div_i(p.n, kBlockN);
   sh.status = p.status;
   sh.tile_counter = p.tile_counter;
+  sh.k_splits = 1;
   auto kern = gemm_tcgen05_pair_kernel<Epi>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
     return check_last("gemm pair smem attribute");
@@ -285,6 +292,7 @@ static int launch_core_bf16(const GemmProblem& p, const Epi& epi, cudaStream_t s
   }
   // A pair of CTAs shares each 256-column B tile, which cuts the operand bytes an SM pulls from L2 per flop by a
   // third; with a single 128-row tile in M the second CTA would only multiply padding.
+  if (p.k_splits > 1) return launch_tcgen05<Epi>(p, epi, stream);   // split-K lives in the single-CTA kernel
   if (p.impl == 2 || (p.impl == 0 && p.m > kBlockM && pair_kernel_enabled()))
     return launch_tcgen05_pair<Epi>(p, epi, stream);
   return launch_tcgen05<Epi>(p, epi, stream);
@@ -318,6 +326,23 @@ static int dispatch_epilogue(const GemmProblem& p, cudaStream_t stream) {
       }
       epi.n = p.n;
       return run(epi);
+    }
+    case kEpiPartialF32: {
+      if constexpr (!Num<T>::kIsBf16) {
+        set_error("split-K partial results are a bf16 tensor-core path");
+        return kErrUnsupported;
+      } else {
+        if (!e.partial || e.ld_partial % 4 != 0 || !aligned16(e.partial)) {
+          set_error("split-K needs a 16-byte aligned partial buffer with a leading dimension that is a multiple of 4");
+          return kErrWorkspace;
+        }
+        EpiPartialF32<T> epi;
+        epi.p = e.partial;
+        epi.ld = e.ld_partial;
+        epi.block_stride = static_cast<int64_t>(p.m) * e.ld_partial;
+        epi.n = p.n;
+        return launch_tcgen05<EpiPartialF32<T>>(p, epi, stream);
+      }
     }
     case kEpiDenseSwiGLU: {
       if (!dense_ok) {

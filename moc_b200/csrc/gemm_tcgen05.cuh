@@ -61,7 +61,32 @@ struct GemmShape {
   int tiles_m, tiles_n;
   int* status;       // device status word
   int* tile_counter; // pair kernel only: zeroed device int; tiles are handed out in arrival order (null: round-robin)
+  int k_splits;      // single-CTA kernel only: > 1 splits the k-blocks of segment 0 over that many tiles; the
+                     // epilogue then sees group * k_splits + split as its group index (one partial result each)
 };
+
+// Which problem, which K range and which output block a tile index stands for.
+struct TileWork {
+  int group, egroup, t, kb_begin, kb_end;
+};
+__device__ __forceinline__ TileWork decode_tile(const GemmShape& sh, int tile, int tiles_per_group, int kb_total) {
+  TileWork w;
+  const int gs = tile / tiles_per_group;
+  w.t = tile - gs * tiles_per_group;
+  if (sh.k_splits > 1) {
+    w.group = gs / sh.k_splits;
+    const int split = gs - w.group * sh.k_splits;
+    const int per = (sh.kb0 + sh.k_splits - 1) / sh.k_splits;
+    w.kb_begin = split * per;
+    w.kb_end = min(sh.kb0, w.kb_begin + per);
+  } else {
+    w.group = gs;
+    w.kb_begin = 0;
+    w.kb_end = kb_total;
+  }
+  w.egroup = gs;
+  return w;
+}
 
 template <class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -79,7 +104,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_per_group = sh.tiles_m * sh.tiles_n;
-  const int num_tiles = tiles_per_group * sh.groups;
+  const int num_tiles = tiles_per_group * sh.groups * (sh.k_splits > 1 ? sh.k_splits : 1);
   const int kb_total = sh.kb0 + sh.kb1;
 
   if (threadIdx.x == 0) {
@@ -116,11 +141,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int group = tile / tiles_per_group;
-        const int t = tile - group * tiles_per_group;
+        const TileWork tw = decode_tile(sh, tile, tiles_per_group, kb_total);
+        const int group = tw.group;
+        const int t = tw.t;
         const int m0 = (t / sh.tiles_n) * kBlockM;
         const int n0 = (t % sh.tiles_n) * kBlockN;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = tw.kb_begin; kb < tw.kb_end; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
@@ -177,7 +203,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
         }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const TileWork tw = decode_tile(sh, tile, tiles_per_group, kb_total);
+        for (int kb = tw.kb_begin; kb < tw.kb_end; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) {
@@ -193,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
           for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {
             const uint64_t da = ptx::make_smem_desc_sw128(a_base + ks * a_step, a_lbo, 1024);
             const uint64_t db = ptx::make_smem_desc_sw128(b_base + ks * b_step, b_lbo, 1024);
-            ptx::umma_bf16_ss(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+            ptx::umma_bf16_ss(d_tmem, da, db, idesc, (kb != tw.kb_begin || ks != 0) ? 1u : 0u);
           }
           ptx::umma_commit(&empty_bar[s]);   // frees the smem stage once these MMAs have read it
         }
@@ -210,8 +237,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       const uint32_t acc = tcount & 1u;
       const uint32_t aph = (tcount >> 1) & 1u;
-      const int group = tile / tiles_per_group;
-      const int t = tile - group * tiles_per_group;
+      const TileWork tw = decode_tile(sh, tile, tiles_per_group, kb_total);
+      const int group = tw.egroup;
+      const int t = tw.t;
       const int m0 = (t / sh.tiles_n) * kBlockM;
       const int col_first = (t % sh.tiles_n) * kBlockN + part * kEpiPartCols;
       const int row = m0 + quad * 32 + lane;

@@ -14,7 +14,7 @@ struct MatOperand {
   int mn_major;   // 0: memory is [mn][k] (K contiguous); 1: memory is [k][mn] (M/N contiguous)
 };
 
-enum EpiKind : int { kEpiStore = 0, kEpiDenseSwiGLU = 2 };
+enum EpiKind : int { kEpiStore = 0, kEpiDenseSwiGLU = 2, kEpiPartialF32 = 3 };
 
 constexpr int kGemmMaxGroups = 3;
 
@@ -29,6 +29,9 @@ struct EpiArgs {
   void* dense1;
   void* dense2;
   int64_t ld_dense;
+  // kEpiPartialF32: [groups * k_splits][m][ld_partial] floats
+  float* partial;
+  int64_t ld_partial;
 };
 
 // C_g[m, n] = A_g[m, k0] * B_g[n, k0]^T for g < groups, or, with groups == 1 and k1 > 0,
@@ -41,6 +44,8 @@ struct GemmProblem {
   int* tile_counter;         // CTA-pair kernel: zeroed device int -> tiles are handed out in arrival order
                              // (null: round-robin over the clusters)
   int sm_reserve;            // CTA-pair kernel: SMs left free for a kernel that runs beside this launch
+  int k_splits;              // > 1 (bf16, kEpiPartialF32 only): K is cut into that many ranges, each tile writes an
+                             // fp32 partial block to epi.partial; the caller adds the blocks up
   int m, n;
   int groups;                // 1..3 same-shape problems in one launch
   int k0;

@@ -967,7 +967,8 @@ int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, c
   const int threads = 128;
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   prof_mark(kProfSel2of8, stream);
-  if (dtype == kBF16 && ldg >= static_cast<int64_t>(words) * 32 && ldg % 8 == 0 &&
+  // one warp per row pays off once there are enough rows to fill the GPU; decode batches keep one thread per word
+  if (dtype == kBF16 && tokens >= 512 && ldg >= static_cast<int64_t>(words) * 32 && ldg % 8 == 0 &&
       (reinterpret_cast<uintptr_t>(g) & 15u) == 0 &&
       (!fuse || (reinterpret_cast<uintptr_t>(fuse->u_dense) & 15u) == 0)) {
     const unsigned vblocks = static_cast<unsigned>((tokens + kVec28Warps - 1) / kVec28Warps);

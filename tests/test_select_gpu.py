@@ -90,7 +90,8 @@ def test_topk_extremes(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("tokens,d_ffn", [(3, 173), (2, 5461), (2, 5464), (4, 8), (1, 9), (1, 11)])
+@pytest.mark.parametrize("tokens,d_ffn", [(3, 173), (2, 5461), (2, 5464), (4, 8), (1, 9), (1, 11), (600, 173),
+                                            (515, 5461)])   # 512 rows and more: the warp-per-row vector kernel
 def test_select_2of8(dtype, tokens, d_ffn):
     g = torch.randn(tokens, d_ffn, generator=torch.Generator().manual_seed(d_ffn)).to(dtype)
     _check(g, None, rule="2of8")
