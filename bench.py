@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8", "dense"],
+    ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs", "dense"],
                     help="dense = the dense SwiGLU comparison row of the same shape")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
     ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
@@ -84,7 +84,7 @@ def cpu_oracle_step_fn(ffn_type):
 
     torch.set_num_threads(os.cpu_count() or 1)
     x, dy, wg, wu, wd = O.make_inputs(CPU_SAMPLE_TOKENS, D, D_FFN, torch.bfloat16, seed=1234)
-    select = "2of8" if ffn_type == "moc_2_8" else "topk"
+    select = {"moc_2_8": "2of8", "moc_post_silu_abs": "post_silu_abs"}.get(ffn_type, "topk")
 
     def step():
         if ffn_type == "dense":

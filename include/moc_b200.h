@@ -42,6 +42,7 @@ extern "C" {
 /* channel selection rule */
 #define MOC_SELECT_TOPK 0   /* global row-wise Top-K on the pre-SiLU gate (moc/ffn.py:144) */
 #define MOC_SELECT_2OF8 1   /* top-2 of every 8 consecutive channels (moc/ffn.py:68-108) */
+#define MOC_SELECT_POST_SILU_ABS 2   /* row-wise Top-K on |SiLU(gate)| (moc/ffn.py:313-369) */
 
 int moc_b200_abi_version(void);
 
@@ -54,8 +55,11 @@ int64_t moc_ffn_ld(int64_t d_ffn);
 int64_t moc_mask_words(int64_t d_ffn);
 int64_t moc_select_2of8_k(int64_t d_ffn);
 
-/* Workspace sizes in bytes for moc_ffn_fwd / moc_ffn_bwd (256-byte aligned base). */
+/* Workspace sizes in bytes for moc_ffn_fwd / moc_ffn_bwd (256-byte aligned base).
+ * moc_ffn_fwd_workspace_bytes covers MOC_SELECT_TOPK and MOC_SELECT_2OF8 (two dense scratch matrices);
+ * MOC_SELECT_POST_SILU_ABS keeps the score matrix as a third one: moc_ffn_fwd_workspace_bytes_select. */
 int64_t moc_ffn_fwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn);
+int64_t moc_ffn_fwd_workspace_bytes_select(int dtype, int select, int64_t tokens, int64_t d_ffn);
 int64_t moc_ffn_bwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn);
 
 /* out[cols, rows] = in[rows, cols]^T. Used to keep W_down^T [d_ffn, d] next to the

@@ -14,7 +14,7 @@ import torch
 LIB_PATH = Path(__file__).resolve().parent / "libmoc_b200.so"
 
 MOC_BF16, MOC_F32 = 0, 1
-SELECT_TOPK, SELECT_2OF8 = 0, 1
+SELECT_TOPK, SELECT_2OF8, SELECT_POST_SILU_ABS = 0, 1, 2
 ERR_DEVICE_TIMEOUT = -6
 
 _DTYPES = {torch.bfloat16: MOC_BF16, torch.float32: MOC_F32}
@@ -28,6 +28,7 @@ SIGNATURES = {
     "moc_mask_words": (c_int64, [c_int64]),
     "moc_select_2of8_k": (c_int64, [c_int64]),
     "moc_ffn_fwd_workspace_bytes": (c_int64, [c_int, c_int64, c_int64]),
+    "moc_ffn_fwd_workspace_bytes_select": (c_int64, [c_int, c_int, c_int64, c_int64]),
     "moc_ffn_bwd_workspace_bytes": (c_int64, [c_int, c_int64, c_int64]),
     "moc_transpose": (c_int, [c_int, _P, _P, c_int64, c_int64, _P]),
     "moc_topk_select": (c_int, [c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, _P, _P, _P, _P]),

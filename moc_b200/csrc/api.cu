@@ -100,6 +100,10 @@ int64_t moc_select_2of8_k(int64_t d_ffn) { return (d_ffn / 8) * 2 + (d_ffn % 8 <
 int64_t moc_ffn_fwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
   return kStatusBytes + 2 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
 }
+int64_t moc_ffn_fwd_workspace_bytes_select(int dtype, int select, int64_t tokens, int64_t d_ffn) {
+  const int dense = select == MOC_SELECT_POST_SILU_ABS ? 3 : 2;
+  return kStatusBytes + dense * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
+}
 int64_t moc_ffn_bwd_workspace_bytes(int dtype, int64_t tokens, int64_t d_ffn) {
   return kStatusBytes + 3 * round_up_i64(tokens * ffn_ld(d_ffn) * (int64_t)esize(dtype), 256);
 }
@@ -167,7 +171,7 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
     set_error("moc_ffn_fwd: null pointer");
     return kErrInvalidArg;
   }
-  if (select != MOC_SELECT_TOPK && select != MOC_SELECT_2OF8) {
+  if (select != MOC_SELECT_TOPK && select != MOC_SELECT_2OF8 && select != MOC_SELECT_POST_SILU_ABS) {
     set_error("moc_ffn_fwd: unknown selection rule %d", select);
     return kErrInvalidArg;
   }
@@ -176,10 +180,10 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
               (long long)moc_select_2of8_k(d_ffn), (long long)d_ffn, (long long)k);
     return kErrInvalidArg;
   }
-  if (workspace_bytes < moc_ffn_fwd_workspace_bytes(dtype, tokens, d_ffn) ||
+  if (workspace_bytes < moc_ffn_fwd_workspace_bytes_select(dtype, select, tokens, d_ffn) ||
       (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
     set_error("moc_ffn_fwd: workspace too small (%lld < %lld bytes) or not 256-byte aligned",
-              (long long)workspace_bytes, (long long)moc_ffn_fwd_workspace_bytes(dtype, tokens, d_ffn));
+              (long long)workspace_bytes, (long long)moc_ffn_fwd_workspace_bytes_select(dtype, select, tokens, d_ffn));
     return kErrWorkspace;
   }
   cudaStream_t stream = as_stream(stream_);
@@ -212,7 +216,18 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   // into the compact saved set and turns the G rows into Z' = mask * round(round(SiLU(G)) * U) in place
   // (moc/ffn.py:156-161, :166-169)
   SelectFuse fuse{u_dense, u_sel, s_sel, z_sel};
-  if (select == MOC_SELECT_TOPK)
+  if (select == MOC_SELECT_POST_SILU_ABS) {
+    // Top-K on |SiLU(G)| (moc/ffn.py:336-339): scores in a third scratch matrix, plain selection on them (the
+    // g_sel array receives scores first), then g, u of the chosen channels are gathered from the dense rows and
+    // the G rows become Z'
+    void* score = static_cast<uint8_t*>(u_dense) + round_up_i64(tokens * ld * (int64_t)esize(dtype), 256);
+    if ((rc = launch_abs_silu(dtype, dense, score, tokens * ld, stream)) != kOk ||
+        (rc = launch_topk_select(dtype, score, ld, (int)tokens, (int)d_ffn, (int)k, nullptr, idx, g_sel, bitmap, rank0,
+                                 stream)) != kOk ||
+        (rc = launch_post_gather(dtype, idx, dense, u_dense, g_sel, u_sel, s_sel, z_sel, ld, (int)tokens, (int)k,
+                                 stream)) != kOk)
+      return rc;
+  } else if (select == MOC_SELECT_TOPK)
     rc = launch_topk_select(dtype, dense, ld, (int)tokens, (int)d_ffn, (int)k, &fuse, idx, g_sel, bitmap, rank0,
                             stream);
   else

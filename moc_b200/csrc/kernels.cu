@@ -804,6 +804,59 @@ expand_z_kernel(const int16_t* __restrict__ idx, const T* __restrict__ z_sel, co
   row_store(zrow, dense + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
 }
 
+// Post-SiLU selection (moc/ffn.py:313-369): the score that Top-K runs on is |SiLU(g)|, rounded to the storage
+// type like the reference's F.silu(g).abs(). SiLU is evaluated with expf and a true division here (the other
+// kernels use the fast forms) so that the scores equal PyTorch's wherever its own exp agrees to the last bit.
+template <typename T>
+__global__ void __launch_bounds__(256)
+abs_silu_kernel(const T* __restrict__ g, T* __restrict__ score, int64_t nvec) {
+  constexpr int E = 16 / sizeof(T);
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const uint4 q = reinterpret_cast<const uint4*>(g)[i];
+  const T* in = reinterpret_cast<const T*>(&q);
+  T out[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const float gv = Num<T>::to_float(in[j]);
+    const float sv = Num<T>::round(gv / (1.0f + expf(-gv)));
+    out[j] = Num<T>::from_float(fabsf(sv));
+  }
+  reinterpret_cast<uint4*>(score)[i] = *reinterpret_cast<const uint4*>(out);
+}
+
+// After a selection that ran on another tensor than the gate: gather g and u of the selected channels from
+// the dense rows, store the compact saved set and replace the dense gate row by Z' (one CTA per token, compact
+// space, shared-memory row image as in bwd_sparse_kernel).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+post_gather_kernel(const int16_t* __restrict__ idx, T* __restrict__ g_dense, const T* __restrict__ u_dense,
+                   T* __restrict__ g_sel, T* __restrict__ u_sel, T* __restrict__ s_sel, T* __restrict__ z_sel,
+                   int64_t ld, int k) {
+  extern __shared__ __align__(16) uint8_t row_smem[];
+  T* zrow = reinterpret_cast<T*>(row_smem);
+  const int row = blockIdx.x;
+  const int64_t crow = static_cast<int64_t>(row) * k;
+  T* grow = g_dense + static_cast<int64_t>(row) * ld;
+  const T* urow = u_dense + static_cast<int64_t>(row) * ld;
+  row_zero(zrow, static_cast<int>(ld));
+  __syncthreads();
+  for (int p = threadIdx.x; p < k; p += kRowThreads) {
+    const int ch = idx[crow + p];
+    const T gv = grow[ch], uv = urow[ch];
+    float s, z;
+    moc_fwd_point<T>(Num<T>::to_float(gv), Num<T>::to_float(uv), s, z);
+    g_sel[crow + p] = gv;
+    u_sel[crow + p] = uv;
+    if (s_sel) s_sel[crow + p] = Num<T>::from_float(s);
+    const T zt = Num<T>::from_float(z);
+    if (z_sel) z_sel[crow + p] = zt;
+    zrow[ch] = zt;
+  }
+  __syncthreads();   // every gather from the gate row is done before the row is overwritten
+  row_store(zrow, grow, static_cast<int>(ld));
+}
+
 // dZ (dense, rounded GEMM output) -> dG', dU' (dense, zero outside the selected channels).
 // dU' overwrites dZ in place, dG' goes to its own buffer.
 // gz = dZ, grad_s = round(u * gz), grad_u = round(s * gz), grad_g = round(grad_s * SiLU'(g)), with
@@ -1023,6 +1076,44 @@ int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void
                                                               static_cast<T*>(dense), ld, k);
   }
   return check_last("expand_z");
+}
+
+int launch_abs_silu(int dtype, const void* g, void* score, int64_t elems, cudaStream_t stream) {
+  if (elems == 0) return kOk;
+  const int64_t nvec = elems * (dtype == kBF16 ? 2 : 4) / 16;
+  const unsigned blocks = static_cast<unsigned>((nvec + 255) / 256);
+  prof_mark(kProfExpand, stream);
+  if (dtype == kBF16)
+    abs_silu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(g),
+                                                              static_cast<__nv_bfloat16*>(score), nvec);
+  else
+    abs_silu_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(g), static_cast<float*>(score), nvec);
+  return check_last("abs_silu");
+}
+
+int launch_post_gather(int dtype, const int16_t* idx, void* g_dense, const void* u_dense, void* g_sel, void* u_sel,
+                       void* s_sel, void* z_sel, int64_t ld, int tokens, int k, cudaStream_t stream) {
+  if (tokens == 0) return kOk;
+  int rc;
+  prof_mark(kProfExpand, stream);
+  if (dtype == kBF16) {
+    const size_t smem = static_cast<size_t>(ld) * 2;
+    auto kern = post_gather_kernel<__nv_bfloat16>;
+    if ((rc = row_smem_setup<__nv_bfloat16>(kern, smem, "post_gather")) != kOk) return rc;
+    kern<<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<__nv_bfloat16*>(g_dense),
+                                                static_cast<const __nv_bfloat16*>(u_dense),
+                                                static_cast<__nv_bfloat16*>(g_sel), static_cast<__nv_bfloat16*>(u_sel),
+                                                static_cast<__nv_bfloat16*>(s_sel), static_cast<__nv_bfloat16*>(z_sel), ld,
+                                                k);
+  } else {
+    const size_t smem = static_cast<size_t>(ld) * 4;
+    auto kern = post_gather_kernel<float>;
+    if ((rc = row_smem_setup<float>(kern, smem, "post_gather")) != kOk) return rc;
+    kern<<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<float*>(g_dense), static_cast<const float*>(u_dense),
+                                                static_cast<float*>(g_sel), static_cast<float*>(u_sel),
+                                                static_cast<float*>(s_sel), static_cast<float*>(z_sel), ld, k);
+  }
+  return check_last("post_gather");
 }
 
 int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,

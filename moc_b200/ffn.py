@@ -68,7 +68,7 @@ def moc_ffn_forward(x2d, gate_w, up_w, down_w_t, k: int, select: int, save_sz: b
     z_sel = torch.empty(tokens, k, device=dev, dtype=dt) if save_sz else None
     bitmap = torch.empty(tokens, words, device=dev, dtype=torch.int32)
     rank0 = torch.empty(tokens, words, device=dev, dtype=torch.int16)
-    ws_bytes = lib.moc_ffn_fwd_workspace_bytes(code, tokens, d_ffn)
+    ws_bytes = lib.moc_ffn_fwd_workspace_bytes_select(code, select, tokens, d_ffn)
     ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
     rc = lib.moc_ffn_fwd(code, select, tokens, d, d_ffn, k, x2d.data_ptr(), gate_w.data_ptr(), up_w.data_ptr(),
                          down_w_t.data_ptr(), y.data_ptr(), idx.data_ptr(), g_sel.data_ptr(), u_sel.data_ptr(),
@@ -249,6 +249,7 @@ class MoCSwiGLUFFN(nn.Module):
     mode='moc' (alias 'moc_triton_aux')         : keep s, z of the selected channels for backward.
     mode='moc_gcp' (alias 'moc_gcp_triton_aux') : recompute them in backward.
     mode='moc_2_8' (alias 'moc_2_8_triton_aux') : structured top-2-of-8 selection; `k` is ignored.
+    mode='moc_post_silu_abs' (alias '..._triton_aux') : Top-K on |SiLU(gate)| instead of the gate (moc/ffn.py:313-369).
     """
 
     def __init__(self, hidden_size: int, intermediate_size: int, k: int | None = None,
@@ -261,10 +262,6 @@ class MoCSwiGLUFFN(nn.Module):
                 "'moc_2_8', 'moc_2_8_triton_aux', "
                 "'moc_post_silu_abs', or 'moc_post_silu_abs_triton_aux'."
             )
-        if mode.startswith("moc_post_silu_abs"):
-            raise NotImplementedError(
-                "mode 'moc_post_silu_abs' (the reference's post-SiLU ablation, moc/ffn.py:313-369) "
-                "has no B200 kernel in this library")
         self.mode = mode
         self.requested_k = k
         if mode.startswith("moc_2_8"):
@@ -306,7 +303,12 @@ class MoCSwiGLUFFN(nn.Module):
             raise ValueError("MoC fused helper kernels require CUDA tensors.")
         compute_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled() else x.dtype
         down_w_t = self._ensure_down_weight_t(compute_dtype)
-        select = _lib.SELECT_2OF8 if self.mode.startswith("moc_2_8") else _lib.SELECT_TOPK
+        if self.mode.startswith("moc_2_8"):
+            select = _lib.SELECT_2OF8
+        elif self.mode.startswith("moc_post_silu_abs"):
+            select = _lib.SELECT_POST_SILU_ABS
+        else:
+            select = _lib.SELECT_TOPK
         y, idx = _MoCB200Function.apply(
             x,
             self.gate_proj.weight,

@@ -109,12 +109,16 @@ def _select(g, k, select):
         return canonical_topk(g, k)
     if select == "2of8":
         return select_2of8(g)
+    if select == "post_silu_abs":
+        # moc/ffn.py:336-339: the K largest |SiLU(g)|; the values handed on are the pre-SiLU gates there
+        _, idx = canonical_topk(F.silu(g).abs(), k)
+        return torch.gather(g, -1, idx), idx
     raise ValueError(select)
 
 
 def moc_forward(x, gate_w, up_w, down_w, k, select="topk", idx_override=None):
     """MoC forward, pure-PyTorch branch of the reference (moc/ffn.py:141-163 for `moc`,
-    :389-414 for `moc_gcp`, :277-298 for `moc_2_8`). All tensors share one dtype (fp32 or
+    :389-414 for `moc_gcp`, :277-298 for `moc_2_8`, :333-354 for `moc_post_silu_abs`). All tensors share one dtype (fp32 or
     bf16); every op rounds to that dtype exactly where the reference's tensor ops do.
 
     ``idx_override`` (int64 [..., k]) replaces the selection step by a given channel set; the

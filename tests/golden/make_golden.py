@@ -5,7 +5,7 @@ Run where the reference checkout is available (it is not shipped with this repos
     python tests/golden/make_golden.py --reference /path/to/MoC
 
 The script imports the reference's own pure-PyTorch modules (``moc.ffn.MoCSwiGLUFFN`` with
-mode "moc" / "moc_gcp" / "moc_2_8", ``moc.inference.inference_ffn.InferenceMoCSwiGLUFFN``
+mode "moc" / "moc_gcp" / "moc_2_8" / "moc_post_silu_abs", ``moc.inference.inference_ffn.InferenceMoCSwiGLUFFN``
 ``masked_reference`` / ``dense_baseline``), runs them on CPU on seeded inputs and writes
 ``*.npz`` files. bf16 arrays are stored as their uint16 bit patterns (suffix ``__bf16``).
 
@@ -93,7 +93,7 @@ def gen_tiny(ref_ffn, dtype, name):
     store = {}
     shape, d, d_ffn, k = (3, 8), 64, 173, 40
     meta = dict(tokens=24, d=d, d_ffn=d_ffn, k=k, seed=1234)
-    for mode in ("moc", "moc_gcp", "moc_2_8"):
+    for mode in ("moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs"):
         canonical = dtype == torch.bfloat16
         out, rec, k_eff = run_training_case(ref_ffn, mode, shape, d, d_ffn, k, dtype, canonical, seed=1234)
         if dtype == torch.float32 and mode != "moc_2_8":

@@ -51,7 +51,7 @@ def _run_gpu(mode, x, grad_y, wg, wu, wd, k):
 
 
 def _oracle(mode, x, grad_y, wg, wu, wd, k, idx_override=None):
-    select = "2of8" if mode.startswith("moc_2_8") else "topk"
+    select = "2of8" if mode.startswith("moc_2_8") else ("post_silu_abs" if mode.startswith("moc_post_silu") else "topk")
     fwd = O.moc_forward(x, wg, wu, wd, k, select=select, idx_override=idx_override)
     if mode.startswith("moc_gcp"):
         grads = O.moc_backward(grad_y, x, wg, wu, wd, fwd["idx"], fwd["g_sel"], fwd["u_sel"])
@@ -86,7 +86,7 @@ SHAPES = [
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8"])
+@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs"])
 @pytest.mark.parametrize("tokens,d,d_ffn,k", SHAPES)
 def test_ffn_matches_oracle_same_mask(dtype, mode, tokens, d, d_ffn, k):
     if dtype == torch.float32 and tokens > 300:
@@ -109,7 +109,7 @@ def test_ffn_matches_oracle_same_mask(dtype, mode, tokens, d, d_ffn, k):
     _compare(got, ref, dtype, f"{mode}[{tokens},{d},{d_ffn},{k}]")
 
 
-@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8"])
+@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs"])
 def test_tiny_fp32_golden(mode):
     """Reference-generated fixture (tests/golden/tiny_fp32.npz): no ties in fp32, so the mask
     itself must match the reference's."""
@@ -122,7 +122,7 @@ def test_tiny_fp32_golden(mode):
     _compare(got, ref, torch.float32, f"golden.{mode}")
 
 
-@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8"])
+@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs"])
 def test_tiny_bf16_golden(mode):
     gold = load_golden("tiny_bf16")
     x, grad_y, wg, wu, wd = O.make_inputs(gold["meta.tokens"], gold["meta.d"], gold["meta.d_ffn"], torch.bfloat16,

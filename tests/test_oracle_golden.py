@@ -16,12 +16,12 @@ def _tiny_inputs(gold, dtype):
 
 
 @pytest.mark.parametrize("dtype,name", [(torch.float32, "tiny_fp32"), (torch.bfloat16, "tiny_bf16")])
-@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8"])
+@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs"])
 def test_training_matches_reference(dtype, name, mode):
     gold = load_golden(name)
     x, grad_y, wg, wu, wd = _tiny_inputs(gold, dtype)
     k = gold["meta.k"]
-    select = "2of8" if mode == "moc_2_8" else "topk"
+    select = {"moc_2_8": "2of8", "moc_post_silu_abs": "post_silu_abs"}.get(mode, "topk")
     fwd = O.moc_forward(x, wg, wu, wd, k, select=select)
     assert fwd["idx"].shape[-1] == gold[f"{mode}.k_effective"]
     # selected channel sets are bit-exact
