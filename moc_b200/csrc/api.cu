@@ -286,11 +286,6 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   void* buf_u = static_cast<uint8_t*>(buf_z) + dense_bytes;          // dZ, then dU'
   void* buf_g = static_cast<uint8_t*>(buf_u) + dense_bytes;          // dG'
 
-  // Z' from the saved (or recomputed) selected activations (moc/ffn.py:196-199, :435-442)
-  if ((rc = launch_expand_z(dtype, idx, z_sel, g_sel, u_sel, buf_z, ld, (int)tokens, (int)d_ffn, (int)k,
-                            stream)) != kOk)
-    return rc;
-
   // dZ = dY W_down (moc/ffn.py:206), rounded to the storage type
   GemmProblem z = problem(dtype, status, tokens, d_ffn, d);
   z.a[0] = operand(grad_y, d, 0);
@@ -299,9 +294,10 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   z.tile_counter = status + kTileCounterFirst;
   if ((rc = launch_gemm(z, stream)) != kOk) return rc;
 
-  // gather through the mask, SiLU', zero fill -> dense dG', dU' (moc/ffn.py:209-237)
-  if ((rc = launch_bwd_sparse(dtype, idx, g_sel, u_sel, buf_u, buf_g, ld, (int)tokens, (int)d_ffn, (int)k,
-                              stream)) != kOk)
+  // one pass over the selected channels: gather through the mask, SiLU', zero fill -> dense dG', dU'
+  // (moc/ffn.py:209-237), and Z' from the saved or recomputed activations (moc/ffn.py:196-199, :435-442)
+  if ((rc = launch_bwd_sparse(dtype, idx, g_sel, u_sel, z_sel, buf_u, buf_g, buf_z, ld, (int)tokens, (int)d_ffn,
+                              (int)k, stream)) != kOk)
     return rc;
 
   // The three weight gradients in one grouped launch, each an [F, d] product over the tokens:

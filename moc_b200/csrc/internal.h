@@ -74,18 +74,17 @@ int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
                        int16_t* idx, void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
 int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, const SelectFuse* fuse, int16_t* idx,
                        void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
-// Z'[tokens, ld] <- zero-filled scatter of the compact z (or of round(round(SiLU(g)) * u) when z_sel is null)
-int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void* g_sel, const void* u_sel, void* dense,
-                    int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
 // score[i] = |round(SiLU(g[i]))| over `elems` elements (a multiple of 128), the selection key of the post-SiLU mode
 int launch_abs_silu(int dtype, const void* g, void* score, int64_t elems, cudaStream_t stream);
 // after a selection on another tensor: compact g_sel, u_sel (+ s_sel, z_sel) from the dense rows; the dense gate
 // rows become Z'
 int launch_post_gather(int dtype, const int16_t* idx, void* g_dense, const void* u_dense, void* g_sel, void* u_sel,
                        void* s_sel, void* z_sel, int64_t ld, int tokens, int k, cudaStream_t stream);
-// dZ[tokens, ld] (in) -> dG' (grad_g_out) and dU' (written over dZ in place): gather, SiLU', zero fill
-int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
-                      void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream);
+// dZ[tokens, ld] (in) -> dG' (grad_g_out) and dU' (written over dZ in place): gather, SiLU', zero fill. z_dense set:
+// also Z'[tokens, ld], the zero-filled scatter of z_sel (or of round(round(SiLU(g)) * u) when z_sel is null)
+int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, const void* z_sel,
+                      void* dz_to_du, void* grad_g_out, void* z_dense, int64_t ld, int tokens, int d_ffn, int k,
+                      cudaStream_t stream);
 // dense SwiGLU backward, elementwise over tokens * ld elements (a multiple of 128)
 int launch_dense_bwd(int dtype, const void* g, const void* u, void* dz_to_du, void* z_out, void* grad_g_out,
                      int64_t elems, cudaStream_t stream);

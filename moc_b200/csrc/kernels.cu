@@ -11,9 +11,9 @@
 //                        saved set and overwrites the gate row by Z' = mask * round(SiLU(G)) * U,
 //                        the operand of the down projection (moc/ffn.py:156-163).
 //   select_2of8_kernel : structured top-2 of every 8 consecutive channels (moc/ffn.py:68-108).
-//   expand_z_kernel    : compact z -> zero-filled dense Z' (moc/ffn.py:196-199, :435-442).
 //   bwd_sparse_kernel  : dense dZ -> zero-filled dense dG', dU' through the selected channels
-//                        (moc/ffn.py:219-237, moc/training/triton_sparse_aux.py:363-423).
+//                        (moc/ffn.py:219-237, moc/training/triton_sparse_aux.py:363-423), and compact z ->
+//                        zero-filled dense Z' (moc/ffn.py:196-199, :435-442) in the same pass.
 //   transpose_kernel   : W_down [d, F] <-> W_down^T [F, d] (moc/inference/inference_ffn.py:104-110).
 #include <cuda_bf16.h>
 #include <stdarg.h>
@@ -758,7 +758,7 @@ __global__ void select_2of8_kernel(T* __restrict__ g, int64_t ldg, int tokens, i
   rank0[gid] = static_cast<uint16_t>(min(w * 8, k_eff));
 }
 
-// The two dense <-> compact kernels below run one CTA per token and work in COMPACT space: every
+// The dense <-> compact kernels below run one CTA per token and work in COMPACT space: every
 // thread handles selected channels only (full lanes for the SiLU math), scatters its results
 // into a zeroed shared-memory image of the dense row, and the CTA then writes the row out
 // with 16-byte coalesced stores.
@@ -776,32 +776,6 @@ __device__ __forceinline__ void row_store(const T* row, T* dst, int ld) {
   uint4* d4 = reinterpret_cast<uint4*>(dst);
   const int nvec = ld * static_cast<int>(sizeof(T)) / 16;
   for (int v = threadIdx.x; v < nvec; v += kRowThreads) d4[v] = r4[v];
-}
-
-// Z'[token, :] = scatter of z_sel (or of round(round(SiLU(g)) * u) when z_sel is null).
-template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
-expand_z_kernel(const int16_t* __restrict__ idx, const T* __restrict__ z_sel, const T* __restrict__ g_sel,
-                const T* __restrict__ u_sel, T* __restrict__ dense, int64_t ld, int k) {
-  extern __shared__ __align__(16) uint8_t row_smem[];
-  T* zrow = reinterpret_cast<T*>(row_smem);
-  const int row = blockIdx.x;
-  const int64_t crow = static_cast<int64_t>(row) * k;
-  row_zero(zrow, static_cast<int>(ld));
-  __syncthreads();
-  for (int p = threadIdx.x; p < k; p += kRowThreads) {
-    const int ch = idx[crow + p];
-    float z;
-    if (z_sel) {
-      z = Num<T>::to_float(z_sel[crow + p]);
-    } else {
-      float s;
-      moc_fwd_point<T>(Num<T>::to_float(g_sel[crow + p]), Num<T>::to_float(u_sel[crow + p]), s, z);
-    }
-    zrow[ch] = Num<T>::from_float(z);
-  }
-  __syncthreads();
-  row_store(zrow, dense + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
 }
 
 // Post-SiLU selection (moc/ffn.py:313-369): the score that Top-K runs on is |SiLU(g)|, rounded to the storage
@@ -858,32 +832,45 @@ post_gather_kernel(const int16_t* __restrict__ idx, T* __restrict__ g_dense, con
 }
 
 // dZ (dense, rounded GEMM output) -> dG', dU' (dense, zero outside the selected channels).
-// dU' overwrites dZ in place, dG' goes to its own buffer.
+// dU' overwrites dZ in place, dG' goes to its own buffer. With z_dense set the same pass also rebuilds the
+// zero-filled Z' rows (from z_sel, or from g and u) that the weight-gradient GEMM of the down projection reads.
 // gz = dZ, grad_s = round(u * gz), grad_u = round(s * gz), grad_g = round(grad_s * SiLU'(g)), with
 // s = round(SiLU(g)) recomputed from g (identical to the saved s of the reference, moc/ffn.py:157).
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 bwd_sparse_kernel(const int16_t* __restrict__ idx, const T* __restrict__ g_sel, const T* __restrict__ u_sel,
-                  T* __restrict__ dz_du, T* __restrict__ grad_g, int64_t ld, int k) {
+                  const T* __restrict__ z_sel, T* __restrict__ dz_du, T* __restrict__ grad_g, T* __restrict__ z_dense,
+                  int64_t ld, int k) {
   extern __shared__ __align__(16) uint8_t row_smem[];
   T* grow = reinterpret_cast<T*>(row_smem);
   T* urow = grow + ld;
+  T* zrow = urow + ld;   // only when z_dense is set
   const int row = blockIdx.x;
   const int64_t crow = static_cast<int64_t>(row) * k;
   T* dzrow = dz_du + static_cast<int64_t>(row) * ld;
-  row_zero(grow, static_cast<int>(2 * ld));
+  row_zero(grow, static_cast<int>((z_dense ? 3 : 2) * ld));
   __syncthreads();
   for (int p = threadIdx.x; p < k; p += kRowThreads) {
     const int ch = idx[crow + p];
+    const float gv = Num<T>::to_float(g_sel[crow + p]), uv = Num<T>::to_float(u_sel[crow + p]);
     float gg, gu;
-    moc_bwd_point<T>(Num<T>::to_float(g_sel[crow + p]), Num<T>::to_float(u_sel[crow + p]),
-                     Num<T>::to_float(dzrow[ch]), gg, gu);
+    moc_bwd_point<T>(gv, uv, Num<T>::to_float(dzrow[ch]), gg, gu);
     grow[ch] = Num<T>::from_float(gg);
     urow[ch] = Num<T>::from_float(gu);
+    if (z_dense) {
+      if (z_sel) {
+        zrow[ch] = z_sel[crow + p];
+      } else {
+        float sv, zv;
+        moc_fwd_point<T>(gv, uv, sv, zv);
+        zrow[ch] = Num<T>::from_float(zv);
+      }
+    }
   }
   __syncthreads();   // all gathers from dZ are done before the row is overwritten
   row_store(grow, grad_g + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
   row_store(urow, dzrow, static_cast<int>(ld));
+  if (z_dense) row_store(zrow, z_dense + static_cast<int64_t>(row) * ld, static_cast<int>(ld));
 }
 
 // Dense SwiGLU backward, elementwise part (autograd of moc/ffn.py:120-121 with stored-dtype tensors):
@@ -1053,31 +1040,6 @@ static int row_smem_setup(Kern kern, size_t smem, const char* what) {
   return kOk;
 }
 
-int launch_expand_z(int dtype, const int16_t* idx, const void* z_sel, const void* g_sel, const void* u_sel, void* dense,
-                    int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream) {
-  (void)d_ffn;
-  if (tokens == 0) return kOk;
-  int rc;
-  if (dtype == kBF16) {
-    using T = __nv_bfloat16;
-    const size_t smem = ld * sizeof(T);
-    if ((rc = row_smem_setup<T>(expand_z_kernel<T>, smem, "expand_z")) != kOk) return rc;
-    prof_mark(kProfExpand, stream);
-    expand_z_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(z_sel),
-                                                              static_cast<const T*>(g_sel), static_cast<const T*>(u_sel),
-                                                              static_cast<T*>(dense), ld, k);
-  } else {
-    using T = float;
-    const size_t smem = ld * sizeof(T);
-    if ((rc = row_smem_setup<T>(expand_z_kernel<T>, smem, "expand_z")) != kOk) return rc;
-    prof_mark(kProfExpand, stream);
-    expand_z_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(z_sel),
-                                                              static_cast<const T*>(g_sel), static_cast<const T*>(u_sel),
-                                                              static_cast<T*>(dense), ld, k);
-  }
-  return check_last("expand_z");
-}
-
 int launch_abs_silu(int dtype, const void* g, void* score, int64_t elems, cudaStream_t stream) {
   if (elems == 0) return kOk;
   const int64_t nvec = elems * (dtype == kBF16 ? 2 : 4) / 16;
@@ -1116,27 +1078,29 @@ int launch_post_gather(int dtype, const int16_t* idx, void* g_dense, const void*
   return check_last("post_gather");
 }
 
-int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, void* dz_to_du,
-                      void* grad_g_out, int64_t ld, int tokens, int d_ffn, int k, cudaStream_t stream) {
+int launch_bwd_sparse(int dtype, const int16_t* idx, const void* g_sel, const void* u_sel, const void* z_sel,
+                      void* dz_to_du, void* grad_g_out, void* z_dense, int64_t ld, int tokens, int d_ffn, int k,
+                      cudaStream_t stream) {
   (void)d_ffn;
   if (tokens == 0) return kOk;
   int rc;
+  const size_t rows = z_dense ? 3 : 2;
   if (dtype == kBF16) {
     using T = __nv_bfloat16;
-    const size_t smem = 2 * ld * sizeof(T);
+    const size_t smem = rows * ld * sizeof(T);
     if ((rc = row_smem_setup<T>(bwd_sparse_kernel<T>, smem, "bwd_sparse")) != kOk) return rc;
     prof_mark(kProfBwdSparse, stream);
-    bwd_sparse_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(g_sel),
-                                                                static_cast<const T*>(u_sel), static_cast<T*>(dz_to_du),
-                                                                static_cast<T*>(grad_g_out), ld, k);
+    bwd_sparse_kernel<T><<<tokens, kRowThreads, smem, stream>>>(
+        idx, static_cast<const T*>(g_sel), static_cast<const T*>(u_sel), static_cast<const T*>(z_sel),
+        static_cast<T*>(dz_to_du), static_cast<T*>(grad_g_out), static_cast<T*>(z_dense), ld, k);
   } else {
     using T = float;
-    const size_t smem = 2 * ld * sizeof(T);
+    const size_t smem = rows * ld * sizeof(T);
     if ((rc = row_smem_setup<T>(bwd_sparse_kernel<T>, smem, "bwd_sparse")) != kOk) return rc;
     prof_mark(kProfBwdSparse, stream);
-    bwd_sparse_kernel<T><<<tokens, kRowThreads, smem, stream>>>(idx, static_cast<const T*>(g_sel),
-                                                                static_cast<const T*>(u_sel), static_cast<T*>(dz_to_du),
-                                                                static_cast<T*>(grad_g_out), ld, k);
+    bwd_sparse_kernel<T><<<tokens, kRowThreads, smem, stream>>>(
+        idx, static_cast<const T*>(g_sel), static_cast<const T*>(u_sel), static_cast<const T*>(z_sel),
+        static_cast<T*>(dz_to_du), static_cast<T*>(grad_g_out), static_cast<T*>(z_dense), ld, k);
   }
   return check_last("bwd_sparse");
 }
