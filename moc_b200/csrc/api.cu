@@ -167,7 +167,9 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   if (bad_dtype(dtype)) return kErrInvalidArg;
   int rc = check_dims(tokens, d, d_ffn, k);
   if (rc != kOk) return rc;
-  if (!x || !w_gate || !w_up || !w_down_t || !y || !idx || !g_sel || !u_sel || !bitmap || !rank0 || !workspace) {
+  // tensors with a token dimension have no storage when tokens == 0
+  if (!w_gate || !w_up || !w_down_t || !workspace ||
+      (tokens > 0 && (!x || !y || !idx || !g_sel || !u_sel || !bitmap || !rank0))) {
     set_error("moc_ffn_fwd: null pointer");
     return kErrInvalidArg;
   }
@@ -253,8 +255,8 @@ int moc_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, int64_t k, 
   if (bad_dtype(dtype)) return kErrInvalidArg;
   int rc = check_dims(tokens, d, d_ffn, k);
   if (rc != kOk) return rc;
-  if (!grad_y || !x || !w_gate || !w_up || !w_down_t || !idx || !g_sel || !u_sel || !grad_x ||
-      !grad_w_gate || !grad_w_up || !grad_w_down || !workspace) {
+  if (!w_gate || !w_up || !w_down_t || !grad_w_gate || !grad_w_up || !grad_w_down || !workspace ||
+      (tokens > 0 && (!grad_y || !x || !idx || !g_sel || !u_sel || !grad_x))) {
     set_error("moc_ffn_bwd: null pointer");
     return kErrInvalidArg;
   }
@@ -347,7 +349,7 @@ int moc_dense_ffn_fwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
   if (bad_dtype(dtype)) return kErrInvalidArg;
   int rc = check_dims(tokens, d, d_ffn, 1);
   if (rc != kOk) return rc;
-  if (!x || !w_gate || !w_up || !w_down_t || !y || !g_out || !u_out || !workspace) {
+  if (!w_gate || !w_up || !w_down_t || !workspace || (tokens > 0 && (!x || !y || !g_out || !u_out))) {
     set_error("moc_dense_ffn_fwd: null pointer");
     return kErrInvalidArg;
   }
@@ -393,8 +395,8 @@ int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
   if (bad_dtype(dtype)) return kErrInvalidArg;
   int rc = check_dims(tokens, d, d_ffn, 1);
   if (rc != kOk) return rc;
-  if (!grad_y || !x || !w_gate || !w_up || !w_down_t || !g || !u || !grad_x || !grad_w_gate || !grad_w_up ||
-      !grad_w_down || !workspace) {
+  if (!w_gate || !w_up || !w_down_t || !grad_w_gate || !grad_w_up || !grad_w_down || !workspace ||
+      (tokens > 0 && (!grad_y || !x || !g || !u || !grad_x))) {
     set_error("moc_dense_ffn_bwd: null pointer");
     return kErrInvalidArg;
   }

@@ -290,3 +290,38 @@ def test_sm_reserve_and_bucketed_gradients():
     assert torch.equal(b[1].view(d_ffn, d), m.gate_proj.weight.grad)
     assert torch.equal(b[2].view(d_ffn, d), m.up_proj.weight.grad)
     assert b.data_ptr() == m.down_proj.weight.grad.data_ptr()      # views, not copies
+
+
+@pytest.mark.parametrize("mode", ["moc", "moc_2_8", "dense"])
+def test_empty_batch(mode):
+    """No tokens: the output is empty, the input gradient is empty and every weight gradient is zero."""
+    d, d_ffn, k = 64, 173, 40
+    m = moc_b200.build_ffn(d, d_ffn, mode, k=k).to(device="cuda", dtype=torch.bfloat16)
+    x = torch.empty(0, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = m(x)
+    assert y.shape == (0, d)
+    y.backward(torch.empty(0, d, device="cuda", dtype=torch.bfloat16))
+    torch.cuda.synchronize()
+    assert x.grad.shape == (0, d)
+    for p in m.parameters():
+        assert p.grad is not None and p.grad.shape == p.shape and not p.grad.any()
+
+
+def test_maximum_d_ffn_and_k_equal_d_ffn():
+    """d_ffn = 32768 is the largest width int16 indices can address (same limit as the reference's packed
+    indices); K = d_ffn selects every channel, so MoC must equal the dense FFN on the same weights."""
+    with pytest.raises(ValueError):
+        MoCSwiGLUFFN(64, 32770, 8, mode="moc")
+    tokens, d, d_ffn = 8, 64, 32768
+    x, grad_y, wg, wu, wd = O.make_inputs(tokens, d, d_ffn, torch.bfloat16, seed=5)
+    got = _run_gpu("moc", x, grad_y, wg, wu, wd, 1024)
+    assert got["idx"].max() < d_ffn and (got["idx"][:, 1:] > got["idx"][:, :-1]).all()
+    ref = _oracle("moc", x, grad_y, wg, wu, wd, 1024, idx_override=got["idx"])
+    _compare(got, ref, torch.bfloat16, "d_ffn=32768")
+    tokens, d, d_ffn = 33, 128, 264
+    x, grad_y, wg, wu, wd = O.make_inputs(tokens, d, d_ffn, torch.bfloat16, seed=6)
+    full = _run_gpu("moc", x, grad_y, wg, wu, wd, d_ffn)
+    assert torch.equal(full["idx"], torch.arange(d_ffn).expand(tokens, d_ffn))
+    y_ref, dx_ref, dg_ref, du_ref, dd_ref = O.dense_forward_backward(x, wg, wu, wd, grad_y)
+    assert rel_l2(full["y"], y_ref) < 1e-2 and rel_l2(full["dx"], dx_ref) < 1e-2
+    assert rel_l2(full["d_gate_w"], dg_ref) < 1e-2 and rel_l2(full["d_down_w"], dd_ref) < 1e-2
