@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
     ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", default="ffn", choices=["ffn", "train_130m", "decode_1b"],
+                    help="ffn: the headline single-layer benchmark (default). train_130m / decode_1b: the end-to-end "
+                         "rows (whole LLaMA-style model around the FFN plugin, moc_b200.host), one JSON line each")
     ap.add_argument("--overlap", type=int, default=1, help="N>1: 1 = start the gradient all-reduce beside the dX GEMM")
     ap.add_argument("--reserve-sms", type=int, default=16, help="N>1 with --overlap: SMs the dX GEMM leaves free")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N>1: cap on the CTAs of an NCCL kernel (0: NCCL default)")
@@ -512,6 +515,110 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_train_130m(args, rank, world, local_rank):
+    """End-to-end training step of the 130m preset (d=768, d_ffn=2048, 12 layers, 12 heads, K=384, vocab 32100,
+    64 x 256 tokens per GPU, synthetic ids with 10 % trailing pad labels, AdamW lr 2.5e-3): forward, loss, backward,
+    optimizer step. Attention, norms, embedding, LM head and the optimizer are PyTorch ops; every FFN is this
+    library's. Data parallel over ranks with DistributedDataParallel."""
+    import torch
+    import torch.distributed as dist
+
+    from moc_b200 import host
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = host.get_config("130m", vocab_size=32100)
+    torch.manual_seed(0)
+    model = host.build_model(cfg, args.ffn_type).to(device=dev, dtype=torch.bfloat16)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank]) if world > 1 else model
+    opt = torch.optim.AdamW(model.parameters(), lr=2.5e-3, betas=(0.9, 0.999), weight_decay=0.0)
+    batch, seq = 64, 256
+    ids, labels = host.synthetic_batch(cfg, batch, seq, pad_fraction=0.1, seed=1234 + rank, device=dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        _, loss = net(ids, labels=labels)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        tokens = batch * seq * world * args.steps
+        print(json.dumps({
+            "metric": "e2e_130m_train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[3]: LLaMA-style 130m model training step, d=768 d_ffn=2048 12 layers 12 heads "
+                                   f"K=384 vocab 32100, 64 x 256 tokens per GPU, AdamW, ffn_type={args.ffn_type}; host ops "
+                                   "(attention, norms, LM head, optimizer) are PyTorch, FFNs are this library",
+                       "parameters": model.num_parameters(), "final_loss": float(loss.item()),
+                       "parallelism": f"DistributedDataParallel x{world}" if world > 1 else "single GPU"},
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_decode_1b(args, rank, world, local_rank):
+    """End-to-end greedy decode of the 1b preset (d=2048, d_ffn=5461, 24 layers, 32 heads, K=1024, vocab 32100,
+    bf16 weights and KV cache, 128 prompt tokens, 256 generated tokens) at batch 1 and 16, every decode step replayed
+    from one CUDA graph. Single GPU."""
+    import torch
+
+    from moc_b200 import host
+
+    if rank != 0:
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    cfg = host.get_config("1b", vocab_size=32100, max_seq_len=384)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = host.build_model(cfg, args.ffn_type).to(dtype=torch.bfloat16).eval()
+    results = {}
+    for batch in (1, 16):
+        prompt = torch.randint(0, cfg.vocab_size, (batch, 128), generator=torch.Generator().manual_seed(7)).to(dev)
+        dec = host.GreedyDecoder(model, batch)
+        dec.generate_graphed(prompt, 8)            # warm-up: allocations, first captures
+        torch.cuda.synchronize()
+        dec = host.GreedyDecoder(model, batch)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = dec.generate_graphed(prompt, 256)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        results[f"b{batch}"] = {"ms_total": ms, "ms_per_token": ms / 256, "tokens_per_s": batch * 256 / (ms * 1e-3),
+                                "generated": list(out.shape)}
+    print(json.dumps({
+        "metric": "e2e_1b_decode_tokens_per_s", "value": results["b1"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+        "steps": 256, "warmup": 8, "ms_per_step": results["b1"]["ms_per_token"], "higher_is_better": True,
+        "scaling": "replicas only", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "configs[4]: 1b model greedy decode, d=2048 d_ffn=5461 24 layers 32 heads K=1024 vocab "
+                               f"32100, prompt 128, 256 new tokens, batch 1 and 16, ffn_type={args.ffn_type}; the timed "
+                               "region includes the prompt pass, the graph capture and 255 graph replays",
+                   "parameters": model.num_parameters()},
+        "batches": results,
+    }), flush=True)
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -525,6 +632,12 @@ def main():
         sys.exit(subprocess.call(cmd))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "train_130m":
+        run_train_130m(args, rank, world, local_rank)
+        return
+    if args.workload == "decode_1b":
+        run_decode_1b(args, rank, world, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -175,6 +175,44 @@ def gen_decode(ref_inf, dtype, name):
     print("wrote", name)
 
 
+def gen_host(ref_model, ref_config):
+    """The reference's LLaMAModel (moc/model.py) on a tiny configuration, fp32, CPU, ffn_type dense and moc:
+    full state_dict, inputs, logits, loss and a few gradients, for the host model of moc_b200.host."""
+    cfg = ref_config.MoCConfig(hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=4,
+                               vocab_size=97, max_seq_len=16, k=40)
+    gen = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab_size, (2, 16), generator=gen)
+    labels = ids.clone()
+    labels[:, 14:] = -100
+    store = {"ids": ids.numpy(), "labels": labels.numpy()}
+    torch.manual_seed(0)
+    base = ref_model.LLaMAModel(cfg, ffn_type="dense")
+    state = {k: v.detach().clone() for k, v in base.state_dict().items()}
+    for k, v in state.items():
+        store["state." + k] = v.numpy()
+    for ffn_type in ("dense", "moc"):
+        m = ref_model.LLaMAModel(cfg, ffn_type=ffn_type)
+        if ffn_type == "moc":
+            # build_ffn picks the Triton helper mode, which needs a GPU; the pure-PyTorch mode is the same function
+            import moc.ffn as ref_ffn
+            for blk in m.blocks:
+                blk.ffn = ref_ffn.MoCSwiGLUFFN(cfg.hidden_size, cfg.intermediate_size, cfg.k, mode="moc")
+        m.load_state_dict(state)
+        rec = TopkRecorder(canonical=False)
+        with mock.patch("torch.topk", rec):
+            logits, loss = m(ids, labels=labels)
+            loss.backward()
+        for g, _, _ in rec.calls:
+            assert not has_threshold_ties(g.reshape(-1, g.shape[-1]), cfg.k), "fp32 host case has ties"
+        store[f"{ffn_type}.logits"] = logits.detach().numpy()
+        store[f"{ffn_type}.loss"] = np.float64(loss.item())
+        for name in ("tok_emb.weight", "blocks.0.ffn.gate_proj.weight", "blocks.1.ffn.down_proj.weight",
+                     "blocks.0.attn.qkv_proj.weight", "lm_head.weight"):
+            store[f"{ffn_type}.grad.{name}"] = dict(m.named_parameters())[name].grad.numpy()
+    np.savez_compressed(HERE / "host_tiny_fp32.npz", **store)
+    print("wrote host_tiny_fp32")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -189,6 +227,9 @@ def main():
     gen_cfg1(ref_ffn)
     gen_decode(ref_inf, torch.float32, "decode_fp32")
     gen_decode(ref_inf, torch.bfloat16, "decode_bf16")
+    import moc.config as ref_config
+    import moc.model as ref_model
+    gen_host(ref_model, ref_config)
 
 
 if __name__ == "__main__":
