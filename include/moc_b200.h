@@ -175,6 +175,12 @@ int moc_decode_2of8(int64_t batch, int64_t d, int64_t d_ffn, const void* x, cons
 int moc_decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const void* w_gate, const void* w_up,
                      const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* sparse_z[b, k] = round(round(SiLU(g_sel[b, k])) * round(x[b, :] . w_up[idx[b, k], :])): the up projection of the
+ * selected channels alone (moc_native::optimized_global_selected_up_silu_bf16,
+ * optimized_global_moc_ext.cu:127-245), with int16 indices. bf16. */
+int moc_decode_selected_up(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* x, const void* g_sel,
+                           const int16_t* idx, const void* w_up, void* sparse_z, void* stream);
+
 /* y[b, :] = sum_k sparse_z[b, k] * w_down_t[idx[b, k], :]: the gathered down projection alone
  * (moc_native::optimized_global_selected_down_bf16, optimized_global_moc_ext.cu:247-372, and
  * moc::selected_grouped_down, triton_grouped_moc_ops.py:96-131), with int16 indices. */

@@ -54,6 +54,7 @@ SIGNATURES = {
     "moc_decode_static_max_d": (c_int64, []),
     "moc_decode_static_max_d_ffn": (c_int64, []),
     "moc_decode_selected_down": (c_int, [c_int64] * 4 + [_P] * 5 + [c_int64, _P]),
+    "moc_decode_selected_up": (c_int, [c_int64] * 4 + [_P] * 6),
 }
 
 _lib = None

@@ -507,6 +507,20 @@ int moc_decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, con
   return decode_dense(batch, d, d_ffn, x, w_gate, w_up, w_down_t, y, workspace, workspace_bytes, as_stream(stream));
 }
 
+int moc_decode_selected_up(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* x, const void* g_sel,
+                           const int16_t* idx, const void* w_up, void* sparse_z, void* stream) {
+  if (batch < 0 || d <= 0 || d % 8 != 0 || d_ffn <= 0 || k <= 0 || k > d_ffn) {
+    set_error("moc_decode_selected_up: bad sizes batch=%lld d=%lld d_ffn=%lld k=%lld", (long long)batch, (long long)d,
+              (long long)d_ffn, (long long)k);
+    return kErrInvalidArg;
+  }
+  if (batch > 0 && (!x || !g_sel || !idx || !w_up || !sparse_z)) {
+    set_error("moc_decode_selected_up: null pointer");
+    return kErrInvalidArg;
+  }
+  return decode_selected_up(batch, k, d, x, g_sel, idx, w_up, sparse_z, as_stream(stream));
+}
+
 int moc_decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* sparse_z,
                              const int16_t* idx, const void* w_down_t, void* y, void* workspace,
                              int64_t workspace_bytes, void* stream) {

@@ -670,6 +670,17 @@ int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const v
   return rc;
 }
 
+int decode_selected_up(int64_t batch, int64_t k, int64_t d, const void* x, const void* g_sel, const int16_t* idx,
+                       const void* w_up, void* z, cudaStream_t stream) {
+  const int64_t total = batch * k;
+  if (total == 0) return kOk;
+  prof_mark(kProfDecodeUp, stream);
+  decode_sel_up_kernel<<<static_cast<unsigned>((total * 32 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const bf16*>(x), static_cast<const bf16*>(g_sel), idx, static_cast<const bf16*>(w_up),
+      static_cast<bf16*>(z), (int)batch, (int)d, (int)k);
+  return check_last("decode_selected_up");
+}
+
 int decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn, const void* z, const int16_t* idx,
                          const void* w_down_t, void* y, void* workspace, int64_t workspace_bytes, cudaStream_t stream) {
   int rc = check_decode_args("moc_decode_selected_down", batch, d, d_ffn, k, workspace, workspace_bytes);

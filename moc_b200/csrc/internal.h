@@ -116,6 +116,8 @@ int launch_decode_fused(int rule, int batch, int d, int d_ffn, int k, const void
                         void* g_scratch, void* seg_scratch, int64_t ld, int* hist, int* status_area,
                         cudaStream_t stream);
 // rule 0: global Top-K, 1: 2-of-8. gate_scores != null: use the caller's [batch, d_ffn] scores instead of x * W_gate^T
+int decode_selected_up(int64_t batch, int64_t k, int64_t d, const void* x, const void* g_sel, const int16_t* idx,
+                       const void* w_up, void* z, cudaStream_t stream);
 int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, const void* x, const void* gate_scores,
                   const void* w_gate, const void* w_up, const void* w_down_t, void* y, void* workspace,
                   int64_t workspace_bytes, cudaStream_t stream);
