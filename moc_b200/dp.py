@@ -38,6 +38,11 @@ class GradAllReducer:
         with reducer:                 # installs the grad-ready hook
             loss.backward()
         # leaving the block waits (stream-wise, not host-wise) for all reductions
+
+    The reduction runs in place on the gradient tensors that the autograd node returns, which become the
+    parameters' ``.grad`` only when those are unset: call ``zero_grad(set_to_none=True)`` before every backward
+    pass. With gradient accumulation into existing ``.grad`` tensors, reduce after the last micro-batch with
+    ``reduce_now`` instead.
     """
 
     def __init__(self, group=None, average: bool = True, overlap: bool = False, reserve_sms: int = 0):
