@@ -145,7 +145,10 @@ int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
  * y[batch, d]. d % 8 == 0. All scratch (gate scores, indices, sparse z, split-K partial sums) lives in
  * `workspace` (moc_decode_workspace_bytes, 256-byte aligned); nothing is allocated. The launches are
  * stream-ordered and capturable in a CUDA graph. Results are deterministic (no floating-point
- * atomics). ---- */
+ * atomics). Batch 1 of the MoC entry points is one cooperative launch of SM-count CTAs that synchronise
+ * through counters in the workspace (bounded waits; moc_read_status reports a time-out): the device
+ * must be able to hold that grid at once, i.e. not be running another kernel that keeps SMs busy
+ * indefinitely. Batches of 16 rows and more (dense: 8) run the projections on the tensor cores. ---- */
 int64_t moc_decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn);
 
 /* Global MoC decode FFN: gate projection, row-wise Top-K (lowest index wins ties), SiLU(g) * (x . W_up
