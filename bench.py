@@ -54,7 +54,11 @@ def parse_args():
     ap.add_argument("--workload", default="ffn", choices=["ffn", "train_130m", "decode_1b"],
                     help="ffn: the headline single-layer benchmark (default). train_130m / decode_1b: the end-to-end "
                          "rows (whole LLaMA-style model around the FFN plugin, moc_b200.host), one JSON line each")
-    ap.add_argument("--overlap", type=int, default=1, help="N>1: 1 = start the gradient all-reduce beside the dX GEMM")
+    ap.add_argument("--overlap", type=int, default=-1,
+                    help="N>1: 1 = start the gradient all-reduce beside the dX GEMM, 0 = after the backward pass, "
+                         "-1 (default) = beside the GEMM on 2 GPUs only: on 4 and 8 GPUs the overlapped collective "
+                         "was faster in most runs (8 GPUs, 32 SMs reserved: 3.06-3.18 against 3.34 ms per step) but "
+                         "single runs took 4-5 ms when its CTAs did not all fit the reserved SMs")
     ap.add_argument("--reserve-sms", type=int, default=16, help="N>1 with --overlap: SMs the dX GEMM leaves free")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N>1: cap on the CTAs of an NCCL kernel (0: NCCL default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -63,13 +67,14 @@ def parse_args():
 
 
 def workload_config(args, world):
+    overlap = args.overlap if args.overlap >= 0 else (1 if world == 2 else 0)
     return {
         "workload": f"configs[1]: single MoC FFN layer fwd+bwd, 1b preset d={D} d_ffn={D_FFN} K={K_SEL}, "
                     f"X[8,2048,{D}] bf16, ffn_type={args.ffn_type}",
         "tokens_per_gpu": args.tokens,
         "global_tokens": args.tokens * world,
         "parallelism": (f"token-sharded dp{world}, one NCCL all-reduce of the three weight gradients per step"
-                        + (f", started beside the dX GEMM ({args.reserve_sms} SMs reserved)" if args.overlap else
+                        + (f", started beside the dX GEMM ({args.reserve_sms} SMs reserved)" if overlap else
                            ", after the backward pass")) if world > 1 else "single GPU",
         "l2": "inputs larger than L2: every step streams >600 MB of activations, weights and scratch "
               "(126 MB L2), no explicit flush",
@@ -316,6 +321,8 @@ def run_ours(args, rank, world, local_rank):
     dy_host = torch.randn(8, tokens // 8, D, generator=gx).bfloat16().pin_memory()
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
+    if args.overlap < 0:
+        args.overlap = 1 if world == 2 else 0
     reducer = (GradAllReducer(average=True, overlap=bool(args.overlap), reserve_sms=args.reserve_sms)
                if world > 1 else None)
 
