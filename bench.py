@@ -43,7 +43,7 @@ CPU_SAMPLE_TOKENS = 1024
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ffn-type", default="moc", choices=["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs", "dense"],
@@ -157,7 +157,7 @@ def run_reference(args, rank, world):
 
 
 class ClockSampler:
-    """Samples nvidia-smi every 50 ms in the background; stop(t0, t1) keeps the samples whose
+    """Samples nvidia-smi every 20 ms in the background; stop(t0, t1) keeps the samples whose
     timestamps fall inside the wall-clock window [t0, t1] (the timed region)."""
 
     QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -171,7 +171,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -389,7 +389,13 @@ def run_ours(args, rank, world, local_rank):
              12: "bwd_sparse"}
     per_kind = {}
     launches = 0
-    for i in range(min(n_prof, cap) - 1):
+    # every FFN call ends with a tag-0 event (forward and backward: two per step); only whole steps are evaluated,
+    # so a profile that filled its event buffer before the last step still gives per-step figures
+    n_rec = min(n_prof, cap)
+    ends = [i for i in range(n_rec) if tags[i] == 0]
+    steps_profiled = len(ends) // 2
+    last = ends[2 * steps_profiled - 1] if steps_profiled else 0
+    for i in range(last):
         tag = tags[i]
         if tag == 0:
             continue
@@ -398,8 +404,8 @@ def run_ours(args, rank, world, local_rank):
         name = kinds.get(tag, f"tag{tag}")
         tot, cnt = per_kind.get(name, (0.0, 0))
         per_kind[name] = (tot + dur, cnt + 1)
-    if n_prof and tags[min(n_prof, cap) - 1] != 0:
-        launches += 1
+    if steps_profiled and steps_profiled != args.steps:
+        launches = round(launches * args.steps / steps_profiled)
     launches += side1 - side0     # tail-row GEMM launches on the side stream (no event)
     peaks, peak_src = load_peaks()
     gemm_ms, gemm_n = per_kind.get("gemm_tcgen05", (0.0, 0))
@@ -407,7 +413,7 @@ def run_ours(args, rank, world, local_rank):
     k_eff = K_SEL
     roofline = None
     if gemm_n:
-        achieved = flops_per_step * args.steps / (gemm_ms * 1e-3) / 1e12
+        achieved = flops_per_step * steps_profiled / (gemm_ms * 1e-3) / 1e12
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         roofline = {
             "bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel", "achieved": achieved, "peak": peak,
@@ -418,7 +424,7 @@ def run_ours(args, rank, world, local_rank):
             # step, from one ncu capture of this workload (2.98 GB per step; 2.22 GB algorithmic)
             "traffic": 0.596e9 if args.ffn_type in ("moc", "moc_gcp") else None,
         }
-    kernel_share = {name: {"ms_per_step": tot / args.steps, "launches_per_step": cnt / args.steps}
+    kernel_share = {name: {"ms_per_step": tot / max(1, steps_profiled), "launches_per_step": cnt / max(1, steps_profiled)}
                     for name, (tot, cnt) in sorted(per_kind.items())}
     if args.dump_kernels and rank == 0:
         # launch-by-launch durations of the last timed step, in launch order
