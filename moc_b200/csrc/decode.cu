@@ -88,7 +88,7 @@ decode_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       uac1[b] = 0.0f;
     }
   }
-#pragma unroll(BT <= 2 ? 8 : 2)
+#pragma unroll(FUSED ? 4 : 8)
   for (int v = lane; v < nvec; v += 32) {
     float a0[8], a1[8], c0[8], c1[8];
     unpack8(wr0[v], a0);
