@@ -215,7 +215,7 @@ def gen_host(ref_model, ref_config):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of xiaohuangji/MoC")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import moc.ffn as ref_ffn  # the reference's own module
