@@ -433,8 +433,12 @@ int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
     return kErrInvalidArg;
   }
   int m_main = 0;
-  SideLane* lane = nullptr;
-  if (!tail_split_rows(p, &m_main) || !(lane = side_lane())) return launch_gemm_whole(p, stream);
+  if (!tail_split_rows(p, &m_main)) return launch_gemm_whole(p, stream);
+  // From here on under the lock: the lane's stream and events are created once and shared by all host threads,
+  // and the fork / join sequence below must not interleave with another thread's.
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideLane* lane = side_lane();
+  if (!lane) return launch_gemm_whole(p, stream);
 
   GemmProblem head = p, tail = p;
   head.m = m_main;
@@ -451,8 +455,6 @@ int launch_gemm(const GemmProblem& p, cudaStream_t stream) {
     __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.epi.c[g]);
     if (c) tail.epi.c[g] = c + (p.epi.transposed[g] ? static_cast<int64_t>(m_main) : static_cast<int64_t>(m_main) * p.epi.ldc[g]);
   }
-  // the fork / join sequence is enqueued under a lock: the lane's events are shared by all host threads
-  std::lock_guard<std::mutex> lock(g_side_mutex);
   if (cudaEventRecord(lane->fork, stream) != cudaSuccess ||
       cudaStreamWaitEvent(lane->stream, lane->fork, 0) != cudaSuccess)
     return check_last("GEMM tail fork");
