@@ -12,6 +12,7 @@ from .ffn import (  # noqa: F401
     set_grad_ready_hook,
     set_status_checks,
 )
+from ._lib import flush_status  # noqa: F401
 
 __all__ = [
     "MoCSwiGLUFFN",
@@ -20,6 +21,7 @@ __all__ = [
     "install_into",
     "set_grad_ready_hook",
     "set_status_checks",
+    "flush_status",
 ]
 
 

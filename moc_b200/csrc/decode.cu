@@ -361,6 +361,7 @@ struct DecodeWs {
   uint32_t* bitmap;  // [batch, words]
   uint16_t* rank0;   // [batch, words]
   float* partial;    // [splits, batch, d]
+  int64_t partial_set_bytes;   // bytes of one split-K partial set of a skinny product (0: batch too small for them)
   int* hist;         // single-launch path: [min(batch, 8), 2048]
   uint16_t* seg;     // single-launch path: compact (channel, z) segments of the CTAs
   int64_t bytes;
@@ -371,9 +372,12 @@ struct DecodeWs {
 constexpr int kDecodeGemmMinBatch = 16;
 constexpr int kDenseGemmMinBatch = 8;
 
-// fp32 bytes of the split-K partial blocks of one skinny product: splits * tiles of 128 rows <= SM count
-static int64_t splitk_partial_bytes(int64_t batch) {
-  return (static_cast<int64_t>(device_sms()) + 2) * 128 * round_up_i64(batch, 4) * 4;
+// fp32 bytes of the split-K partial blocks of one skinny product over `rows` weight rows: splits * tiles of 128
+// rows <= SM count while the tiles fit the SMs, one block of round_up(rows, 128) rows (splits = 1) beyond that
+static int64_t splitk_partial_bytes(int64_t batch, int64_t rows) {
+  const int64_t by_sms = (static_cast<int64_t>(device_sms()) + 2) * 128;
+  const int64_t by_rows = round_up_i64(rows, 128);
+  return (by_sms > by_rows ? by_sms : by_rows) * round_up_i64(batch, 4) * 4;
 }
 
 static int64_t partial_bound(int64_t batch, int64_t d, int64_t d_ffn) {
@@ -382,7 +386,8 @@ static int64_t partial_bound(int64_t batch, int64_t d, int64_t d_ffn) {
   const int64_t by_cap = batch * ((d_ffn + kDownMaxRows - 1) / kDownMaxRows + 1);
   const int64_t gather = (by_target > by_cap ? by_target : by_cap) * d * 4;
   // batches that go through the split-K GEMMs keep two partial sets (gate and up of the dense baseline)
-  const int64_t skinny = batch >= kDenseGemmMinBatch ? 2 * round_up_i64(splitk_partial_bytes(batch), 256) : 0;
+  const int64_t skinny =
+      batch >= kDenseGemmMinBatch ? 2 * round_up_i64(splitk_partial_bytes(batch, d_ffn > d ? d_ffn : d), 256) : 0;
   return gather > skinny ? gather : skinny;
 }
 
@@ -406,6 +411,8 @@ static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
   w.bitmap = reinterpret_cast<uint32_t*>(take(batch * words * 4));
   w.rank0 = reinterpret_cast<uint16_t*>(take(batch * words * 2));
   w.partial = reinterpret_cast<float*>(take(partial_bound(batch, d, d_ffn)));
+  w.partial_set_bytes =
+      batch >= kDenseGemmMinBatch ? round_up_i64(splitk_partial_bytes(batch, d_ffn > d ? d_ffn : d), 256) : 0;
   w.seg = reinterpret_cast<uint16_t*>(take(decode_fused_seg_words(batch < 8 ? batch : 8, d_ffn) * 2));
   w.bytes = p - static_cast<uint8_t*>(base);
   return w;
@@ -455,7 +462,7 @@ static int skinny_splits(int rows, int k) {
 }
 
 static int skinny_gemm(const bf16* a, int64_t lda, int a_mn, const bf16* bt, int64_t ldb, int rows, int batch, int k,
-                       float* partial, int* splits_out, int* status, cudaStream_t stream) {
+                       float* partial, int64_t partial_bytes, int* splits_out, int* status, cudaStream_t stream) {
   GemmProblem p = {};
   p.dtype = kBF16;
   p.status = status;
@@ -474,26 +481,30 @@ static int skinny_gemm(const bf16* a, int64_t lda, int a_mn, const bf16* bt, int
   p.epi.partial = partial;
   p.epi.ld_partial = round_up_i64(batch, 4);
   *splits_out = p.k_splits;
+  if (static_cast<int64_t>(p.k_splits) * round_up_i64(rows, 128) * p.epi.ld_partial * 4 > partial_bytes) {
+    set_error("decode: split-K partial blocks (%d x %d rows) exceed their workspace region", p.k_splits, rows);
+    return kErrWorkspace;
+  }
   return launch_gemm(p, stream);
 }
 
 // out[b, f] = round(x[b, :] . W[f, :]) for every row of W: CUDA-core GEMV for small batches, split-K tensor-core
 // product plus reduction for batches of 16 rows and more.
 static int project_rows(const bf16* x, const bf16* w, bf16* out, int64_t ld_out, int batch, int d, int rows,
-                        int* status, float* partial, cudaStream_t stream) {
+                        int* status, float* partial, int64_t partial_bytes, cudaStream_t stream) {
   if (batch < kDecodeGemmMinBatch) return launch_gemv<false>(x, w, nullptr, out, ld_out, batch, d, rows, stream);
   int splits = 1;
-  int rc = skinny_gemm(w, d, 0, x, d, rows, batch, d, partial, &splits, status, stream);
+  int rc = skinny_gemm(w, d, 0, x, d, rows, batch, d, partial, partial_bytes, &splits, status, stream);
   if (rc != kOk) return rc;
   return launch_skinny_consume<0>(partial, nullptr, splits, rows, batch, out, ld_out, rows, nullptr, 0, nullptr, 0, stream);
 }
 
 // y[b, :] = round(sum over f of Z'[b, f] * W_down^T[f, :]) from dense zero-filled Z' rows (leading dimension ld)
 static int down_dense(const bf16* z_dense, int64_t ld, const bf16* w_down_t, bf16* y, int batch, int d, int d_ffn,
-                      int* status, float* partial, cudaStream_t stream) {
+                      int* status, float* partial, int64_t partial_bytes, cudaStream_t stream) {
   int splits = 1;
   prof_mark(kProfDecodeDown, stream);
-  int rc = skinny_gemm(w_down_t, d, 1, z_dense, ld, d, batch, d_ffn, partial, &splits, status, stream);
+  int rc = skinny_gemm(w_down_t, d, 1, z_dense, ld, d, batch, d_ffn, partial, partial_bytes, &splits, status, stream);
   if (rc != kOk) return rc;
   return launch_skinny_consume<0>(partial, nullptr, splits, d, batch, y, d, d, nullptr, 0, nullptr, 0, stream);
 }
@@ -528,15 +539,19 @@ static int selected_tail(const DecodeWs& w, const bf16* x, const bf16* scores, i
     int splits = 1;
     float* up_partial = w.partial;
     prof_mark(kProfDecodeUp, stream);
-    if ((rc = skinny_gemm(w_up, d, 0, x, d, d_ffn, batch, d, up_partial, &splits, w.status, stream)) != kOk) return rc;
+    if ((rc = skinny_gemm(w_up, d, 0, x, d, d_ffn, batch, d, up_partial, w.partial_set_bytes, &splits, w.status,
+                          stream)) != kOk)
+      return rc;
     if ((rc = launch_skinny_consume<1>(up_partial, nullptr, splits, d_ffn, batch, w.u, ld, static_cast<int>(ld), scores,
                                        ld_scores, w.bitmap, static_cast<int>(mask_words(d_ffn)), stream)) != kOk)
       return rc;
-    return down_dense(w.u, ld, w_down_t, y, batch, d, d_ffn, w.status, w.partial, stream);
+    return down_dense(w.u, ld, w_down_t, y, batch, d, d_ffn, w.status, w.partial, w.partial_set_bytes, stream);
   }
   if (total > d_ffn) {
     // the batch selects more rows than W_up has: one dense pass over W_up, then pick
-    if ((rc = project_rows(x, w_up, w.u, ffn_ld(d_ffn), batch, d, d_ffn, w.status, w.partial, stream)) != kOk) return rc;
+    if ((rc = project_rows(x, w_up, w.u, ffn_ld(d_ffn), batch, d, d_ffn, w.status, w.partial, w.partial_set_bytes,
+                           stream)) != kOk)
+      return rc;
     prof_mark(kProfDecodeUp, stream);
     decode_z_from_u_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(w.u, ffn_ld(d_ffn), w.g_sel,
                                                                                          w.idx, w.z, batch, k);
@@ -613,7 +628,7 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
     scores = const_cast<void*>(gate_scores);
     ld_scores = d_ffn;
   } else if ((rc = project_rows(xb, static_cast<const bf16*>(w_gate), w.gate, ld_scores, (int)batch, (int)d,
-                                (int)d_ffn, w.status, w.partial, stream)) != kOk) {
+                                (int)d_ffn, w.status, w.partial, w.partial_set_bytes, stream)) != kOk) {
     return rc;
   }
   if (rule == 0)
@@ -642,19 +657,19 @@ int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const v
     const int64_t ld = ffn_ld(d_ffn);
     const bf16* xb = static_cast<const bf16*>(x);
     float* g_partial = w.partial;
-    float* u_partial = w.partial + round_up_i64(splitk_partial_bytes(batch), 256) / 4;
+    float* u_partial = w.partial + w.partial_set_bytes / 4;
     int splits = 1, splits_u = 1;
     prof_mark(kProfDecodeDense, stream);
     if ((rc = skinny_gemm(static_cast<const bf16*>(w_gate), d, 0, xb, d, (int)d_ffn, (int)batch, (int)d, g_partial,
-                          &splits, w.status, stream)) != kOk ||
+                          w.partial_set_bytes, &splits, w.status, stream)) != kOk ||
         (rc = skinny_gemm(static_cast<const bf16*>(w_up), d, 0, xb, d, (int)d_ffn, (int)batch, (int)d, u_partial,
-                          &splits_u, w.status, stream)) != kOk)
+                          w.partial_set_bytes, &splits_u, w.status, stream)) != kOk)
       return rc;
     if ((rc = launch_skinny_consume<1>(u_partial, g_partial, splits, (int)d_ffn, (int)batch, w.u, ld, static_cast<int>(ld),
                                        nullptr, 0, nullptr, 0, stream)) != kOk)
       return rc;
     rc = down_dense(w.u, ld, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), (int)batch, (int)d, (int)d_ffn,
-                    w.status, w.partial, stream);
+                    w.status, w.partial, w.partial_set_bytes, stream);
     prof_mark(kProfEnd, stream);
     return rc;
   }

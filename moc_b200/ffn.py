@@ -44,8 +44,9 @@ def transpose_weight(w: torch.Tensor) -> torch.Tensor:
     _lib.require_cuda(w)
     w = w.contiguous()
     out = torch.empty(w.shape[1], w.shape[0], device=w.device, dtype=w.dtype)
-    _lib.check(_lib.lib().moc_transpose(_lib.dtype_code(w.dtype), w.data_ptr(), out.data_ptr(), w.shape[0],
-                                        w.shape[1], _lib.stream_ptr(w.device)), "moc_transpose")
+    with torch.cuda.device(w.device):
+        _lib.check(_lib.lib().moc_transpose(_lib.dtype_code(w.dtype), w.data_ptr(), out.data_ptr(), w.shape[0],
+                                            w.shape[1], _lib.stream_ptr(w.device)), "moc_transpose")
     return out
 
 
@@ -70,13 +71,20 @@ def moc_ffn_forward(x2d, gate_w, up_w, down_w_t, k: int, select: int, save_sz: b
     rank0 = torch.empty(tokens, words, device=dev, dtype=torch.int16)
     ws_bytes = lib.moc_ffn_fwd_workspace_bytes_select(code, select, tokens, d_ffn)
     ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
-    rc = lib.moc_ffn_fwd(code, select, tokens, d, d_ffn, k, x2d.data_ptr(), gate_w.data_ptr(), up_w.data_ptr(),
+    with torch.cuda.device(dev):       # the library launches on the current device
+        rc = _call_fwd(lib, code, select, tokens, d, d_ffn, k, x2d, gate_w, up_w, down_w_t, y, idx, g_sel, u_sel, s_sel,
+                       z_sel, bitmap, rank0, ws, ws_bytes, dev)
+    _lib.check(rc, "moc_ffn_fwd")
+    _maybe_check_status(ws, dev, "moc_ffn_fwd")
+    return y, idx, g_sel, u_sel, s_sel, z_sel, bitmap, rank0
+
+
+def _call_fwd(lib, code, select, tokens, d, d_ffn, k, x2d, gate_w, up_w, down_w_t, y, idx, g_sel, u_sel, s_sel, z_sel,
+              bitmap, rank0, ws, ws_bytes, dev):
+    return lib.moc_ffn_fwd(code, select, tokens, d, d_ffn, k, x2d.data_ptr(), gate_w.data_ptr(), up_w.data_ptr(),
                          down_w_t.data_ptr(), y.data_ptr(), idx.data_ptr(), g_sel.data_ptr(), u_sel.data_ptr(),
                          _lib.ptr(s_sel), _lib.ptr(z_sel), bitmap.data_ptr(), rank0.data_ptr(), ws.data_ptr(),
                          ws_bytes, _lib.stream_ptr(dev))
-    _lib.check(rc, "moc_ffn_fwd")
-    _maybe_check_status(ws, dev)
-    return y, idx, g_sel, u_sel, s_sel, z_sel, bitmap, rank0
 
 
 def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, idx, g_sel, u_sel, s_sel, z_sel,
@@ -103,13 +111,14 @@ def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, idx, g_sel, u_sel, s
     evs = [None, None, None]
     if grad_events is not None:
         evs = [e.cuda_event if e is not None else None for e in grad_events]
-    rc = lib.moc_ffn_bwd(code, tokens, d, d_ffn, k, grad_y2d.data_ptr(), x2d.data_ptr(), gate_w.data_ptr(),
-                         up_w.data_ptr(), down_w_t.data_ptr(), idx.data_ptr(), g_sel.data_ptr(),
-                         u_sel.data_ptr(), _lib.ptr(s_sel), _lib.ptr(z_sel), dx.data_ptr(), d_gate.data_ptr(),
-                         d_up.data_ptr(), d_down.data_ptr(), ws.data_ptr(), ws_bytes, evs[0], evs[1], evs[2],
-                         _lib.stream_ptr(dev))
+    with torch.cuda.device(dev):       # the library launches on the current device
+        rc = lib.moc_ffn_bwd(code, tokens, d, d_ffn, k, grad_y2d.data_ptr(), x2d.data_ptr(), gate_w.data_ptr(),
+                             up_w.data_ptr(), down_w_t.data_ptr(), idx.data_ptr(), g_sel.data_ptr(),
+                             u_sel.data_ptr(), _lib.ptr(s_sel), _lib.ptr(z_sel), dx.data_ptr(), d_gate.data_ptr(),
+                             d_up.data_ptr(), d_down.data_ptr(), ws.data_ptr(), ws_bytes, evs[0], evs[1], evs[2],
+                             _lib.stream_ptr(dev))
     _lib.check(rc, "moc_ffn_bwd")
-    _maybe_check_status(ws, dev)
+    _maybe_check_status(ws, dev, "moc_ffn_bwd")
     return dx, d_gate, d_up, d_down, bucket
 
 
@@ -118,14 +127,19 @@ _CHECK_STATUS = False
 
 def set_status_checks(enabled: bool) -> None:
     """When enabled, every op synchronises and raises if a kernel recorded a bounded-wait
-    time-out (costs a stream sync per call; meant for tests and debugging)."""
+    time-out (costs a stream sync per call; meant for tests and debugging). When disabled (the default) the
+    same check runs asynchronously and raises one call later (moc_b200._lib.watch_status)."""
     global _CHECK_STATUS
     _CHECK_STATUS = bool(enabled)
 
 
-def _maybe_check_status(ws: torch.Tensor, dev) -> None:
+def _maybe_check_status(ws: torch.Tensor, dev, what: str = "moc_b200 call") -> None:
+    """Time-out detection after a call that used workspace ``ws``: synchronous when ``set_status_checks(True)``,
+    otherwise through the asynchronous status ring (raises at the next call, or at ``flush_status``)."""
     if _CHECK_STATUS:
         _lib.check(_lib.lib().moc_read_status(ws.data_ptr(), _lib.stream_ptr(dev)), "device status")
+    else:
+        _lib.watch_status(ws, what)
 
 
 # ------------------------------------------------------------------------------------------
@@ -189,7 +203,8 @@ class _MoCB200Function(torch.autograd.Function):
         ctx.x_dtype = x.dtype
         ctx.w_dtypes = (gate_w.dtype, up_w.dtype, down_w.dtype)
         ctx.mark_non_differentiable(idx)
-        return y.reshape(x.shape).to(x.dtype), idx.reshape(*x.shape[:-1], k)
+        # like the reference's matmuls under autocast, the output has the compute dtype (moc/ffn.py:163)
+        return y.reshape(x.shape), idx.reshape(*x.shape[:-1], k)
 
     @staticmethod
     def backward(ctx, grad_out, _grad_idx):
@@ -211,9 +226,12 @@ class _MoCB200Function(torch.autograd.Function):
         d_gate = d_gate.to(ctx.w_dtypes[0])
         d_up = d_up.to(ctx.w_dtypes[1])
         d_down = d_down.to(ctx.w_dtypes[2])
-        if hook is not None and events is None:
+        if hook is not None and (events is None or not same_dtype):
+            # after the last backward kernel; also when the gradients were converted to another parameter dtype:
+            # the converted tensors are written by cast kernels queued behind the dX GEMM, so the early events
+            # (recorded behind the weight-gradient GEMM) do not cover them
             done = torch.cuda.Event()
-            done.record()          # after the last backward kernel
+            done.record()
             events = (done, done, done)
         if hook is not None and same_dtype:
             hook("bucket", bucket, events[2])      # one collective over the three gradients (views of `bucket`)
@@ -237,10 +255,26 @@ class StandardSwiGLUFFN(nn.Module):
         self.gate_proj = nn.Linear(hidden_size, intermediate_size, bias=False)
         self.up_proj = nn.Linear(hidden_size, intermediate_size, bias=False)
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
+        # W_down^T [d_ffn, d] copy the kernels read, refreshed whenever the parameter changes (as in MoCSwiGLUFFN)
+        self._down_weight_t: torch.Tensor | None = None
+        self._down_weight_t_key = None
+
+    def _ensure_down_weight_t(self, dtype: torch.dtype) -> torch.Tensor:
+        w = self.down_proj.weight
+        key = (w.data_ptr(), w._version, dtype, w.device)
+        if self._down_weight_t is None or self._down_weight_t_key != key:
+            with torch.no_grad():
+                self._down_weight_t = transpose_weight(w.detach().to(dtype))
+            self._down_weight_t_key = key
+        return self._down_weight_t
 
     def forward(self, x):
         from .dense import dense_swiglu
-        return dense_swiglu(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)
+        if not x.is_cuda:
+            raise ValueError("The B200 dense SwiGLU kernels require CUDA tensors.")
+        compute_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled() else x.dtype
+        return dense_swiglu(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight,
+                            self._ensure_down_weight_t(compute_dtype))
 
 
 class MoCSwiGLUFFN(nn.Module):

@@ -225,6 +225,10 @@ class GreedyDecoder:
 
     def __init__(self, model: HostLlama, batch: int, mode: str = "auto"):
         cfg = model.config
+        if model.ffn_type == "moc_post_silu_abs":
+            # the decode kernels select on the raw gate; a model trained with Top-K on |SiLU(gate)| would decode
+            # with another channel set than its forward pass (the reference has no such decode mode either)
+            raise ValueError("GreedyDecoder does not support ffn_type='moc_post_silu_abs'")
         self.model = model
         self.mode = mode
         self.batch = batch

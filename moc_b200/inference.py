@@ -165,7 +165,9 @@ class InferenceMoCSwiGLUFFN(nn.Module):
             args.append(self.config.k)
         args += [x_2d.data_ptr(), wg.data_ptr(), wu.data_ptr(), wdt.data_ptr(), y.data_ptr(), ws.data_ptr(),
                  ws.numel(), _lib.stream_ptr(x_2d.device)]
-        _lib.check(getattr(lib, fn_name)(*args), fn_name)
+        with torch.cuda.device(x_2d.device):       # the library launches on the current device
+            _lib.check(getattr(lib, fn_name)(*args), fn_name)
+        _lib.watch_status(ws, fn_name)             # asynchronous time-out check (skipped during graph capture)
         return self._restore_output_shape(y, original_shape)
 
     def dense_baseline(self, x: torch.Tensor) -> torch.Tensor:

@@ -82,6 +82,27 @@ def test_decode_2of8_and_dense(batch, d, d_ffn):
     _close(gotd, refd, 1e-2, f"dense[{batch},{d},{d_ffn}]")
 
 
+@pytest.mark.parametrize("batch", [8, 64])
+def test_decode_dense_widest_d_ffn(batch):
+    """d_ffn = 32768 (the widest the int16 channel indices address) with a small hidden size: here the split-K
+    products of the dense baseline have more 128-row tiles than the device has SMs, so each keeps a single
+    partial block of d_ffn rows; the gate and up blocks must not overlap and must stay inside the workspace.
+    A canary behind the workspace must survive."""
+    d, d_ffn = 64, 32768
+    x, _, wg, wu, wd = O.make_inputs(batch, d, d_ffn, BF, seed=batch)
+    n = _lib.lib().moc_decode_workspace_bytes(batch, d, d_ffn)
+    buf = torch.full((n + 4096,), 0x5A, device="cuda", dtype=torch.uint8)
+    y = torch.full((batch, d), float("nan"), device="cuda", dtype=BF)
+    xc, wgc, wuc = x.cuda(), wg.cuda(), wu.cuda()
+    wdt = transpose_weight(wd.cuda())
+    _lib.check(_lib.lib().moc_decode_dense(batch, d, d_ffn, xc.data_ptr(), wgc.data_ptr(), wuc.data_ptr(),
+                                           wdt.data_ptr(), y.data_ptr(), buf.data_ptr(), n, _lib.stream_ptr()),
+               "moc_decode_dense")
+    torch.cuda.synchronize()
+    assert bool((buf[n:] == 0x5A).all()), "write beyond the workspace"
+    _close(y.cpu(), O.dense_baseline(x, wg, wu, wd), 1e-2, f"dense[{batch},{d},{d_ffn}]")
+
+
 def test_decode_golden_fixture():
     """tests/golden/decode_bf16.npz: the reference's masked_reference / dense_baseline on CPU."""
     gold = load_golden("decode_bf16")

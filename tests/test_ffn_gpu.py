@@ -124,18 +124,29 @@ def test_tiny_fp32_golden(mode):
 
 @pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8", "moc_post_silu_abs"])
 def test_tiny_bf16_golden(mode):
+    """Reference-generated bf16 fixture (tests/golden/tiny_bf16.npz, canonical tie rule). The GPU's gate
+    scores may differ from the CPU's by one bf16 ulp, which can swap a near-tie channel in a few rows, so the
+    comparison never depends on full index agreement: (a) token rows whose channel set equals the fixture's are
+    compared with the fixture's y and dX rows; (b) every output is compared with the oracle evaluated under the
+    GPU's own channel sets (the oracle itself is pinned to this fixture by tests/test_oracle_golden.py)."""
     gold = load_golden("tiny_bf16")
     x, grad_y, wg, wu, wd = O.make_inputs(gold["meta.tokens"], gold["meta.d"], gold["meta.d_ffn"], torch.bfloat16,
                                            seed=gold["meta.seed"])
     got = _run_gpu(mode, x, grad_y, wg, wu, wd, gold["meta.k"])
     ref_idx = gold[f"{mode}.idx_sorted"].to(torch.int64)
+    same_rows = (got["idx"] == ref_idx).all(dim=1)
     agree = (got["idx"] == ref_idx).float().mean().item()
-    print(f"golden bf16 {mode}: index agreement {agree:.4f}")
-    if agree == 1.0:
+    print(f"golden bf16 {mode}: index agreement {agree:.4f}, {int(same_rows.sum())} of {same_rows.numel()} rows equal")
+    assert agree > 0.95 and same_rows.float().mean().item() >= 0.5
+    for key in ("y", "dx"):
+        r = rel_l2(got[key][same_rows], gold[f"{mode}.{key}"][same_rows])
+        print(f"golden.{mode}.{key} (rows with the fixture's channel set): rel_l2={r:.3e}")
+        assert r <= BF16_REL
+    if bool(same_rows.all()):
         ref = {key: gold[f"{mode}.{key}"] for key in ("y", "dx", "d_gate_w", "d_up_w", "d_down_w")}
         _compare(got, ref, torch.bfloat16, f"golden.{mode}")
-    else:
-        assert agree > 0.95
+    ref = _oracle(mode, x, grad_y, wg, wu, wd, gold["meta.k"], idx_override=got["idx"])
+    _compare(got, ref, torch.bfloat16, f"golden-inputs.{mode}")
 
 
 def test_cfg1_golden():
@@ -325,3 +336,50 @@ def test_maximum_d_ffn_and_k_equal_d_ffn():
     y_ref, dx_ref, dg_ref, du_ref, dd_ref = O.dense_forward_backward(x, wg, wu, wd, grad_y)
     assert rel_l2(full["y"], y_ref) < 1e-2 and rel_l2(full["dx"], dx_ref) < 1e-2
     assert rel_l2(full["d_gate_w"], dg_ref) < 1e-2 and rel_l2(full["d_down_w"], dd_ref) < 1e-2
+
+
+def _run_dense_gpu(x, grad_y, wg, wu, wd):
+    d, d_ffn = x.shape[-1], wg.shape[0]
+    m = build_ffn(d, d_ffn, "dense").to(device="cuda", dtype=x.dtype)
+    with torch.no_grad():
+        m.gate_proj.weight.copy_(wg)
+        m.up_proj.weight.copy_(wu)
+        m.down_proj.weight.copy_(wd)
+    xs = x.cuda().requires_grad_(True)
+    moc_b200.set_status_checks(True)
+    try:
+        y = m(xs)
+        y.backward(grad_y.cuda())
+    finally:
+        moc_b200.set_status_checks(False)
+    torch.cuda.synchronize()
+    return dict(y=y.detach().cpu(), dx=xs.grad.cpu(), d_gate_w=m.gate_proj.weight.grad.cpu(),
+                d_up_w=m.up_proj.weight.grad.cpu(), d_down_w=m.down_proj.weight.grad.cpu())
+
+
+@pytest.mark.parametrize("mode", ["moc", "moc_gcp", "moc_2_8", "dense"])
+def test_benchmarked_shape_matches_oracle(mode):
+    """The benchmarked configuration itself (1b preset: d=2048, d_ffn=5461, K=1024, bf16; shape from
+    benchmarks/training/benchmark_training_latency.py:20-22) against the CPU oracle, with a ragged token count so
+    that the launches with a partial last row tile (and the side-stream tail of the weight-gradient product) run.
+    Same tolerances as the small shapes; max-abs and relative L2 are printed per tensor."""
+    tokens, d, d_ffn, k = 1157, 2048, 5461, 1024
+    x, grad_y, wg, wu, wd = O.make_inputs(tokens, d, d_ffn, torch.bfloat16, seed=1234)
+    label = f"{mode}[{tokens},{d},{d_ffn},{k}]"
+    if mode == "dense":
+        got = _run_dense_gpu(x, grad_y, wg, wu, wd)
+        ref = O.dense_forward_backward(x, wg, wu, wd, grad_y)
+        _compare(got, dict(zip(("y", "dx", "d_gate_w", "d_up_w", "d_down_w"), ref)), torch.bfloat16, label)
+        return
+    got = _run_gpu(mode, x, grad_y, wg, wu, wd, k)
+    k_eff = got["idx"].shape[-1]
+    assert k_eff == (O.effective_k_2of8(d_ffn) if mode == "moc_2_8" else k)
+    assert (got["idx"][:, 1:] > got["idx"][:, :-1]).all() and got["idx"].min() >= 0 and got["idx"].max() < d_ffn
+    own = _oracle(mode, x, grad_y, wg, wu, wd, k)
+    both = torch.zeros(tokens, d_ffn, dtype=torch.bool).scatter_(1, got["idx"], True) & \
+        torch.zeros(tokens, d_ffn, dtype=torch.bool).scatter_(1, own["idx"], True)
+    agree = both.sum().item() / (tokens * k_eff)
+    print(f"{label}: mask agreement with the oracle's own gate {agree:.5f}")
+    assert agree >= 0.98
+    ref = _oracle(mode, x, grad_y, wg, wu, wd, k, idx_override=got["idx"])
+    _compare(got, ref, torch.bfloat16, label)

@@ -37,7 +37,8 @@ def _static_call(batch, d, d_ffn, k, x, wg, wu, wdt):
 
 
 def test_static_scratch_entry_matches_workspace_entry_twice():
-    for call, (batch, d, d_ffn, k, seed) in enumerate([(8, 2048, 5461, 1024, 11), (3, 256, 1000, 200, 12)]):
+    for call, (batch, d, d_ffn, k, seed) in enumerate([(8, 2048, 5461, 1024, 11), (3, 256, 1000, 200, 12),
+                                                        (1, 2048, 5461, 1024, 13), (1, 256, 1000, 200, 14)]):
         x, _, wg, wu, wd = O.make_inputs(batch, d, d_ffn, BF, seed=seed)
         xc, wgc, wuc = x.cuda(), wg.cuda(), wu.cuda()
         wdt = transpose_weight(wd.cuda())
