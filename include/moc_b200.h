@@ -145,10 +145,14 @@ int moc_dense_ffn_bwd(int dtype, int64_t tokens, int64_t d, int64_t d_ffn, const
  * y[batch, d]. d % 8 == 0. All scratch (gate scores, indices, sparse z, split-K partial sums) lives in
  * `workspace` (moc_decode_workspace_bytes, 256-byte aligned); nothing is allocated. The launches are
  * stream-ordered and capturable in a CUDA graph. Results are deterministic (no floating-point
- * atomics). Batch 1 of the MoC entry points is one cooperative launch of SM-count CTAs that synchronise
- * through counters in the workspace (bounded waits; moc_read_status reports a time-out): the device
- * must be able to hold that grid at once, i.e. not be running another kernel that keeps SMs busy
- * indefinitely. Batches of 16 rows and more (dense: 8) run the projections on the tensor cores. ---- */
+ * atomics). Batches of up to 8 rows (d a multiple of 256 up to 2048, at most 48 channels per SM, weights
+ * 16-byte aligned) run as ONE persistent launch of SM-count CTAs, preceded by a small kernel that clears the
+ * status area: every CTA streams the W_gate, W_up and W_down^T rows of its own channels once through a
+ * shared-memory ring, and the CTAs synchronise through counters in the workspace (bounded waits;
+ * moc_read_status reports a time-out): the device must be able to hold that grid at once, i.e. not be running
+ * another kernel that keeps SMs busy indefinitely. Other shapes and batches of 9 to 15 rows use separate
+ * streaming kernels per projection; batches of 16 rows and more (dense: 8) that the persistent launch does
+ * not take run the projections on the tensor cores. ---- */
 int64_t moc_decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn);
 
 /* Global MoC decode FFN: gate projection, row-wise Top-K (lowest index wins ties), SiLU(g) * (x . W_up
@@ -194,7 +198,7 @@ int moc_decode_selected_down(int64_t batch, int64_t k, int64_t d, int64_t d_ffn,
 /* Global MoC decode FFN without any caller-provided scratch: same computation and same result as
  * moc_decode_global, for callers that must not allocate device memory when they call (a fixed memory
  * budget that is already handed out, a frozen allocator in a serving loop, a runtime that passes a
- * plugin nothing but its inputs and outputs). The scratch is a fixed 6 MiB array inside the library's
+ * plugin nothing but its inputs and outputs). The scratch is a fixed 12 MiB array inside the library's
  * device image, present on every GPU that loads the library for the life of the process. No counterpart
  * in the reference (its decode ops allocate their outputs and temporaries with torch::empty,
  * moc/inference/cuda/optimized_global_moc_ext.cu:468-472).
@@ -235,6 +239,19 @@ int moc_set_overlap_sm_reserve(int sms);
 /* Synchronises `stream` and returns MOC_OK, or MOC_ERR_DEVICE_TIMEOUT if a kernel of the
  * last call that used `workspace` recorded a bounded-wait failure in its status area. */
 int moc_read_status(const void* workspace, void* stream);
+
+/* Test hook: limit, in SM clock cycles, of the bounded grid-barrier waits of the persistent decode kernel
+ * (copy-completion waits keep their fixed limit, so that no CTA leaves with a copy in flight). Process-wide; cycles <= 0 restores the default (about 0.2 s). A wait that runs out makes
+ * the kernel return early with the status word set (moc_read_status / moc_publish_status report it); nothing traps
+ * or spins forever. No counterpart in the reference. */
+int moc_debug_set_wait_cycles(int64_t cycles);
+
+/* Asynchronous form of the same check: enqueues a one-thread kernel on `stream` that copies the status word of
+ * `workspace` to *host_word if it is non-zero. host_word must be pinned host memory that the device can address
+ * (cudaHostAlloc / cudaMallocHost; with unified addressing its host pointer is valid on the device). The caller
+ * polls *host_word from the host at its own pace; no synchronisation, no copy-engine transfer, capturable in a
+ * CUDA graph. No counterpart in the reference (its kernels have no bounded waits). */
+int moc_publish_status(const void* workspace, int* host_word, void* stream);
 
 #ifdef __cplusplus
 }

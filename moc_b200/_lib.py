@@ -42,6 +42,8 @@ SIGNATURES = {
     "moc_side_launch_count": (c_int64, []),
     "moc_set_overlap_sm_reserve": (c_int, [c_int]),
     "moc_read_status": (c_int, [_P, _P]),
+    "moc_publish_status": (c_int, [_P, _P, _P]),
+    "moc_debug_set_wait_cycles": (c_int, [c_int64]),
     "moc_dense_ffn_fwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 8 + [c_int64, _P]),
     "moc_dense_ffn_bwd": (c_int, [c_int, c_int64, c_int64, c_int64] + [_P] * 12 + [c_int64, _P]),
     "moc_decode_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
@@ -112,81 +114,59 @@ def stream_ptr(device=None) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-class _StatusRing:
-    """Always-on detection of bounded-wait time-outs without a host synchronisation.
+class _StatusSink:
+    """Always-on detection of bounded-wait time-outs without a host synchronisation and without a copy.
 
     Every kernel wait of the library is bounded; a wait that runs out sets the status word at the start of
     the call's workspace and the kernel returns early, leaving its outputs incomplete. After each call the
-    wrappers copy that word into a small ring of pinned host slots (one asynchronous 4-byte copy on the
-    caller's stream plus an event); at the next call the slots whose events have completed are read, and a
-    non-zero word raises ``RuntimeError`` (MOC_ERR_DEVICE_TIMEOUT), at the latest one call after the failure.
-    ``flush`` synchronises and checks everything that is pending. Nothing is enqueued while the stream is being
-    captured into a CUDA graph."""
-
-    SLOTS = 16
+    wrappers enqueue ``moc_publish_status``: a one-thread kernel that stores a non-zero status word into one
+    pinned host word per device (the GPU reaches pinned host memory directly; nothing is written in the normal
+    case, and no copy engine is involved, so the check never queues behind a large transfer). At the next call
+    the host word is read, and a non-zero word raises ``RuntimeError`` (MOC_ERR_DEVICE_TIMEOUT). Calls
+    recorded into a CUDA graph are not followed by the publish kernel (replays are unchecked)."""
 
     def __init__(self, device):
         self.device = device
-        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
-        self.events = [None] * self.SLOTS
-        self.what = [""] * self.SLOTS
-        self.next = 0
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.view = self.host.numpy()
+        self.what = ""
 
-    def _check_slot(self, i: int, wait: bool) -> None:
-        ev = self.events[i]
-        if ev is None:
-            return
-        if wait:
-            ev.synchronize()
-        elif not ev.query():
-            return
-        self.events[i] = None
-        word = int(self.host[i])
+    def check(self) -> None:
+        word = int(self.view[0])
         if word != 0:
-            self.host[i] = 0
+            self.view[0] = 0
             raise RuntimeError(
-                f"{self.what[i]} failed with code {ERR_DEVICE_TIMEOUT}: device-side wait timed out "
+                f"{self.what or 'a moc_b200 call'} failed with code {ERR_DEVICE_TIMEOUT}: device-side wait timed out "
                 f"(role {(word >> 24) & 0xFF}, detail 0x{word & 0xFFFFFF:x}); the outputs of that call are incomplete")
 
-    def poll(self) -> None:
-        for i in range(self.SLOTS):
-            self._check_slot(i, wait=False)
-
     def push(self, ws: torch.Tensor, what: str) -> None:
+        self.check()
         if torch.cuda.is_current_stream_capturing():
-            return
-        self.poll()
-        i = self.next
-        self._check_slot(i, wait=True)       # the ring wrapped around a copy that is still in flight
-        self.next = (i + 1) % self.SLOTS
-        self.host[i:i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(self.device))
-        self.events[i] = ev
-        self.what[i] = what
-
-    def flush(self) -> None:
-        for i in range(self.SLOTS):
-            self._check_slot(i, wait=True)
+            return      # a dependent one-thread node would cost a decode graph about 2 us per FFN call
+        with torch.cuda.device(self.device):
+            check(lib().moc_publish_status(ws.data_ptr(), self.host.data_ptr(), stream_ptr(self.device)),
+                  "moc_publish_status")
+        self.what = what
 
 
-_rings: dict = {}
+_sinks: dict = {}
 
 
 def watch_status(ws: torch.Tensor, what: str) -> None:
     """Queue the status word of the call that just used workspace ``ws`` for the asynchronous time-out check and
     raise for any earlier call whose word came back non-zero."""
     key = ws.device.index
-    ring = _rings.get(key)
-    if ring is None:
-        ring = _rings[key] = _StatusRing(ws.device)
-    ring.push(ws, what)
+    sink = _sinks.get(key)
+    if sink is None:
+        sink = _sinks[key] = _StatusSink(ws.device)
+    sink.push(ws, what)
 
 
 def flush_status() -> None:
-    """Wait for every queued status word and raise if one reports a time-out."""
-    for ring in _rings.values():
-        ring.flush()
+    """Wait for the queued work of every device that ran a call and raise if one reported a time-out."""
+    for sink in _sinks.values():
+        torch.cuda.synchronize(sink.device)
+        sink.check()
 
 
 def require_cuda(*tensors: torch.Tensor) -> None:

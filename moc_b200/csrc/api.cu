@@ -85,6 +85,11 @@ int record(void* ev, cudaStream_t stream) {
   return kOk;
 }
 
+__global__ void publish_status_kernel(const int* __restrict__ status, volatile int* host_word) {
+  const int w = *status;
+  if (w != 0) *host_word = w;
+}
+
 }  // namespace
 
 extern "C" {
@@ -568,6 +573,20 @@ int moc_read_status(const void* workspace, void* stream_) {
     return kErrDeviceTimeout;
   }
   return kOk;
+}
+
+int moc_debug_set_wait_cycles(int64_t cycles) {
+  decode_stream_set_wait_cycles(static_cast<long long>(cycles));
+  return kOk;
+}
+
+int moc_publish_status(const void* workspace, int* host_word, void* stream_) {
+  if (!workspace || !host_word) {
+    set_error("moc_publish_status: null pointer");
+    return kErrInvalidArg;
+  }
+  publish_status_kernel<<<1, 1, 0, as_stream(stream_)>>>(static_cast<const int*>(workspace), host_word);
+  return check_last("moc_publish_status");
 }
 
 }  // extern "C"

@@ -362,8 +362,7 @@ struct DecodeWs {
   uint16_t* rank0;   // [batch, words]
   float* partial;    // [splits, batch, d]
   int64_t partial_set_bytes;   // bytes of one split-K partial set of a skinny product (0: batch too small for them)
-  int* hist;         // single-launch path: [min(batch, 8), 2048]
-  uint16_t* seg;     // single-launch path: compact (channel, z) segments of the CTAs
+  int* hist;         // single-launch path: [min(batch, 8), 2048] key histograms
   int64_t bytes;
 };
 
@@ -388,7 +387,12 @@ static int64_t partial_bound(int64_t batch, int64_t d, int64_t d_ffn) {
   // batches that go through the split-K GEMMs keep two partial sets (gate and up of the dense baseline)
   const int64_t skinny =
       batch >= kDenseGemmMinBatch ? 2 * round_up_i64(splitk_partial_bytes(batch, d_ffn > d ? d_ffn : d), 256) : 0;
-  return gather > skinny ? gather : skinny;
+  // the single persistent launch keeps one fp32 partial output per CTA
+  const bool stream = decode_stream_supported(batch, d, d_ffn, 0) || decode_stream_supported(batch, d, d_ffn, 1) ||
+                      decode_stream_supported(batch, d, d_ffn, 2);
+  const int64_t persistent = stream ? decode_stream_partial_bytes(batch, d) : 0;
+  const int64_t m = gather > skinny ? gather : skinny;
+  return m > persistent ? m : persistent;
 }
 
 static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
@@ -402,7 +406,7 @@ static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
   };
   w.status = reinterpret_cast<int*>(take(256));
   // directly behind the status area: one memset clears both before a single-launch call
-  w.hist = reinterpret_cast<int*>(take(decode_fused_hist_bytes(batch < 8 ? batch : 8)));
+  w.hist = reinterpret_cast<int*>(take((batch < 8 ? batch : 8) * 2048 * 4));
   w.gate = reinterpret_cast<bf16*>(take(batch * ld * 2));
   w.u = reinterpret_cast<bf16*>(take(batch * ld * 2));
   w.idx = reinterpret_cast<int16_t*>(take(batch * d_ffn * 2));
@@ -413,7 +417,6 @@ static DecodeWs carve(void* base, int64_t batch, int64_t d, int64_t d_ffn) {
   w.partial = reinterpret_cast<float*>(take(partial_bound(batch, d, d_ffn)));
   w.partial_set_bytes =
       batch >= kDenseGemmMinBatch ? round_up_i64(splitk_partial_bytes(batch, d_ffn > d ? d_ffn : d), 256) : 0;
-  w.seg = reinterpret_cast<uint16_t*>(take(decode_fused_seg_words(batch < 8 ? batch : 8, d_ffn) * 2));
   w.bytes = p - static_cast<uint8_t*>(base);
   return w;
 }
@@ -583,26 +586,19 @@ static int check_decode_args(const char* who, int64_t batch, int64_t d, int64_t 
   return kOk;
 }
 
-// MOC_B200_DECODE_FUSED=0 in the environment keeps small batches on the multi-kernel path (a switch for A/B timing).
-static bool fused_decode_enabled() {
+// MOC_B200_DECODE_STREAM=0 in the environment keeps small batches off the persistent streaming launch (a switch for
+// A/B timing against the older paths).
+static bool stream_decode_enabled() {
   static int v = -1;
   if (v < 0) {
-    const char* e = getenv("MOC_B200_DECODE_FUSED");
+    const char* e = getenv("MOC_B200_DECODE_STREAM");
     v = (e && e[0] == '0') ? 0 : 1;
   }
   return v == 1;
 }
-
-// The single launch wins at batch 1 (measured at the 1b shape, inside CUDA graphs: 27 against 30 us for the Top-K
-// rule, 22 against 29 us for 2:8); from batch 2 on its per-row work in shared memory makes the multi-kernel path
-// faster. MOC_B200_DECODE_FUSED_MAX_BATCH (1..8) overrides the limit for experiments.
-static int64_t fused_decode_max_batch() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("MOC_B200_DECODE_FUSED_MAX_BATCH");
-    v = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 1;
-  }
-  return v;
+// bulk copies read whole weight rows: the matrices must start on 16-byte boundaries (rows are d * 2 bytes, d % 256 == 0)
+static bool aligned16(const void* a, const void* b, const void* c) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0;
 }
 
 int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, const void* x, const void* gate_scores,
@@ -612,15 +608,15 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
   if (rc != kOk) return rc;
   if (batch == 0) return kOk;
   const DecodeWs w = carve(workspace, batch, d, d_ffn);
-  if (fused_decode_enabled() && batch <= fused_decode_max_batch() && decode_fused_supported(batch, d, d_ffn)) {
-    // very small batches: the whole FFN in one cooperative launch
-    rc = launch_decode_fused(rule, (int)batch, (int)d, (int)d_ffn, (int)k, x, gate_scores, d_ffn, w_gate, w_up,
-                             w_down_t, y, w.gate, w.seg, ffn_ld(d_ffn), w.hist, w.status, stream);
+  if (stream_decode_enabled() && decode_stream_supported(batch, d, d_ffn, rule) &&
+      aligned16(gate_scores ? w_up : w_gate, w_up, w_down_t) && (reinterpret_cast<uintptr_t>(x) & 3u) == 0) {
+    // up to 8 rows: the whole FFN in one persistent launch that streams every weight row once
+    rc = launch_decode_stream(rule, (int)batch, (int)d, (int)d_ffn, (int)k, x, gate_scores, d_ffn, w_gate, w_up,
+                              w_down_t, y, w.gate, ffn_ld(d_ffn), w.hist, w.status, w.partial, stream);
     prof_mark(kProfEnd, stream);
     return rc;
   }
-  if (batch >= kDecodeGemmMinBatch && cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess)
-    return check_last("cudaMemsetAsync");
+  if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
   const bf16* xb = static_cast<const bf16*>(x);
   void* scores = w.gate;
   int64_t ld_scores = ffn_ld(d_ffn);
@@ -651,9 +647,16 @@ int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const v
   if (rc != kOk) return rc;
   if (batch == 0) return kOk;
   const DecodeWs w = carve(workspace, batch, d, d_ffn);
+  if (stream_decode_enabled() && decode_stream_supported(batch, d, d_ffn, 2) && aligned16(w_gate, w_up, w_down_t) &&
+      (reinterpret_cast<uintptr_t>(x) & 3u) == 0) {
+    rc = launch_decode_stream(2, (int)batch, (int)d, (int)d_ffn, (int)d_ffn, x, nullptr, 0, w_gate, w_up, w_down_t, y,
+                              w.gate, ffn_ld(d_ffn), w.hist, w.status, w.partial, stream);
+    prof_mark(kProfEnd, stream);
+    return rc;
+  }
+  if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
   if (batch >= kDenseGemmMinBatch) {
     // three skinny tensor-core products; SwiGLU is applied while the gate and up partial blocks are reduced
-    if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
     const int64_t ld = ffn_ld(d_ffn);
     const bf16* xb = static_cast<const bf16*>(x);
     float* g_partial = w.partial;

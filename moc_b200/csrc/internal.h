@@ -105,16 +105,18 @@ void prof_mark(int tag, cudaStream_t stream);
 
 // ---- decode path (decode.cu), bf16 only ---------------------------------------------------------
 int64_t decode_workspace_bytes(int64_t batch, int64_t d, int64_t d_ffn);
-// Single-launch decode for batches of up to 8 rows (decode_fused.cu). g_scratch: [batch, ld] bf16; seg_scratch:
-// decode_fused_seg_words(batch, d_ffn) 16-bit words; hist: decode_fused_hist_bytes(batch) bytes; status_area:
-// 64 ints ([0] status word, [32] barrier counter).
-bool decode_fused_supported(int64_t batch, int64_t d, int64_t d_ffn);
-int64_t decode_fused_hist_bytes(int64_t batch);
-int64_t decode_fused_seg_words(int64_t batch, int64_t d_ffn);
-int launch_decode_fused(int rule, int batch, int d, int d_ffn, int k, const void* x, const void* scores,
-                        int64_t ld_scores, const void* w_gate, const void* w_up, const void* w_down_t, void* y,
-                        void* g_scratch, void* seg_scratch, int64_t ld, int* hist, int* status_area,
-                        cudaStream_t stream);
+// Single persistent launch for batches of up to 8 rows (decode_stream.cu): every CTA streams the W_gate, W_up and
+// W_down^T rows of its own channels through a shared-memory ring. rule 0: Top-K, 1: 2-of-8, 2: dense baseline.
+// g_scratch: [batch, ld] bf16; hist: [batch, 2048] ints directly behind the 256-byte status area (status word at
+// [0], barrier counter at [32]); partial: decode_stream_partial_bytes(batch, d) bytes.
+bool decode_stream_supported(int64_t batch, int64_t d, int64_t d_ffn, int rule);
+int64_t decode_stream_partial_bytes(int64_t batch, int64_t d);
+int launch_decode_stream(int rule, int batch, int d, int d_ffn, int k, const void* x, const void* scores,
+                         int64_t ld_scores, const void* w_gate, const void* w_up, const void* w_down_t, void* y,
+                         void* g_scratch, int64_t ld, int* hist, int* status_area, float* partial,
+                         cudaStream_t stream);
+// limit (cycles) of the bounded grid-barrier waits of the persistent decode kernel; <= 0 restores the default
+void decode_stream_set_wait_cycles(long long cycles);
 // rule 0: global Top-K, 1: 2-of-8. gate_scores != null: use the caller's [batch, d_ffn] scores instead of x * W_gate^T
 int decode_selected_up(int64_t batch, int64_t k, int64_t d, const void* x, const void* g_sel, const int16_t* idx,
                        const void* w_up, void* z, cudaStream_t stream);

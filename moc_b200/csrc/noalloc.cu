@@ -3,8 +3,8 @@
 // Some hosts of this library may not allocate device memory at the point where they need an FFN
 // evaluated: code running under a memory budget that was handed out completely at start-up, a
 // serving loop whose allocator is frozen once the weights and caches are placed, or a plugin that is
-// only given input and output buffers by its runtime. moc_decode_global needs a few hundred kilobytes
-// of scratch (gate scores, selected indices, sparse activations, split-K partial sums) from such a
+// only given input and output buffers by its runtime. moc_decode_global needs up to about ten megabytes
+// of scratch (gate scores, histograms, one partial output vector per SM and batch row) from such a
 // caller; this variant keeps that scratch inside the library instead, in a fixed array in device
 // memory that every GPU loading the library holds until the process exits.
 #include <cuda_runtime.h>
@@ -21,7 +21,7 @@ namespace {
 constexpr int64_t kStaticMaxBatch = 8;
 constexpr int64_t kStaticMaxD = 4096;
 constexpr int64_t kStaticMaxDffn = 8192;
-constexpr size_t kStaticScratchBytes = 6u << 20;   // 6 MiB per GPU
+constexpr size_t kStaticScratchBytes = 12u << 20;   // 12 MiB per GPU
 
 // The scratch itself. In host code this name is only a stand-in for the symbol, not a device address;
 // the address is obtained once per device with cudaGetSymbolAddress below.

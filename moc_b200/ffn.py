@@ -135,7 +135,7 @@ def set_status_checks(enabled: bool) -> None:
 
 def _maybe_check_status(ws: torch.Tensor, dev, what: str = "moc_b200 call") -> None:
     """Time-out detection after a call that used workspace ``ws``: synchronous when ``set_status_checks(True)``,
-    otherwise through the asynchronous status ring (raises at the next call, or at ``flush_status``)."""
+    otherwise through the pinned status word of the device (raises at the next call, or at ``flush_status``)."""
     if _CHECK_STATUS:
         _lib.check(_lib.lib().moc_read_status(ws.data_ptr(), _lib.stream_ptr(dev)), "device status")
     else:

@@ -167,7 +167,7 @@ class InferenceMoCSwiGLUFFN(nn.Module):
                  ws.numel(), _lib.stream_ptr(x_2d.device)]
         with torch.cuda.device(x_2d.device):       # the library launches on the current device
             _lib.check(getattr(lib, fn_name)(*args), fn_name)
-        _lib.watch_status(ws, fn_name)             # asynchronous time-out check (skipped during graph capture)
+        _lib.watch_status(ws, fn_name)             # asynchronous time-out check (one tiny launch; not recorded into graphs)
         return self._restore_output_shape(y, original_shape)
 
     def dense_baseline(self, x: torch.Tensor) -> torch.Tensor:

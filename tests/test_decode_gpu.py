@@ -103,6 +103,37 @@ def test_decode_dense_widest_d_ffn(batch):
     _close(y.cpu(), O.dense_baseline(x, wg, wu, wd), 1e-2, f"dense[{batch},{d},{d_ffn}]")
 
 
+def test_bounded_wait_runs_out_and_the_next_call_recovers():
+    """Every device-side wait of the library is bounded. With the grid-barrier limit lowered to one cycle
+    (moc_debug_set_wait_cycles) the persistent decode kernel's first barrier gives up in the CTAs that do not
+    arrive last: the kernel must return (no trap, no endless spin), the status word must report the time-out
+    through both the synchronous and the asynchronous reader, and the next call with the normal limit must be
+    correct again."""
+    lib = _lib.lib()
+    batch, d, d_ffn, k = 1, 2048, 5461, 1024
+    x, _, wg, wu, wd = O.make_inputs(batch, d, d_ffn, BF, seed=5)
+    xc, wgc, wuc = x.cuda(), wg.cuda(), wu.cuda()
+    wdt = transpose_weight(wd.cuda())
+    y = torch.zeros(batch, d, device="cuda", dtype=BF)
+    ws = _ws(batch, d, d_ffn)
+    sink = torch.zeros(1, dtype=torch.int32).pin_memory()
+    args = [batch, d, d_ffn, k, xc.data_ptr(), wgc.data_ptr(), wuc.data_ptr(), wdt.data_ptr(), y.data_ptr(),
+            ws.data_ptr(), ws.numel(), _lib.stream_ptr()]
+    _lib.check(lib.moc_debug_set_wait_cycles(1), "moc_debug_set_wait_cycles")
+    try:
+        _lib.check(lib.moc_decode_global(*args), "moc_decode_global")
+        _lib.check(lib.moc_publish_status(ws.data_ptr(), sink.data_ptr(), _lib.stream_ptr()), "moc_publish_status")
+        rc = lib.moc_read_status(ws.data_ptr(), _lib.stream_ptr())
+    finally:
+        lib.moc_debug_set_wait_cycles(0)
+    assert rc == _lib.ERR_DEVICE_TIMEOUT and "timed out" in _lib.last_error()
+    torch.cuda.synchronize()
+    assert int(sink[0]) != 0
+    _lib.check(lib.moc_decode_global(*args), "moc_decode_global")
+    assert lib.moc_read_status(ws.data_ptr(), _lib.stream_ptr()) == 0
+    _close(y.cpu(), O.masked_reference(x, wg, wu, wd, k=k), 5e-2, "after a time-out")
+
+
 def test_decode_golden_fixture():
     """tests/golden/decode_bf16.npz: the reference's masked_reference / dense_baseline on CPU."""
     gold = load_golden("decode_bf16")
