@@ -319,6 +319,9 @@ class MoCSwiGLUFFN(nn.Module):
         # W_down's own rows); refreshed whenever the parameter changes, never saved.
         self._down_weight_t: torch.Tensor | None = None
         self._down_weight_t_key = None
+        # record_topk_idx = True keeps the selected channel indices [..., k] (int16) of the latest forward call in
+        # last_topk_idx, for inspection and tests; off by default: it would pin tokens * k * 2 bytes per layer
+        self.record_topk_idx = False
         self.last_topk_idx: torch.Tensor | None = None
         # True: also write and keep s_sel, z_sel like the reference's `moc` mode (moc/ffn.py:166-169)
         self.materialize_sz = False
@@ -353,7 +356,7 @@ class MoCSwiGLUFFN(nn.Module):
             select,
             not self.materialize_sz,
         )
-        self.last_topk_idx = idx
+        self.last_topk_idx = idx if self.record_topk_idx else None
         return y
 
 

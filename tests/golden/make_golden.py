@@ -213,23 +213,85 @@ def gen_host(ref_model, ref_config):
     print("wrote host_tiny_fp32")
 
 
+def gen_decoder(reference_dir):
+    """The reference's static-cache decoder (benchmarks/inference/benchmark_decode.py:312-362: DecoderModel with
+    forward_prompt / forward_step_static) on a tiny configuration, bf16, CPU, with its FFNs evaluated by their
+    dense-masking definition (masked_reference, canonical tie rule): state_dict, prompt, and the logits and greedy
+    token of every decode step, for moc_b200.host.GreedyDecoder. Row kinds: dense and global_moc."""
+    import importlib.util
+
+    path = Path(reference_dir) / "benchmarks" / "inference" / "benchmark_decode.py"
+    spec = importlib.util.spec_from_file_location("ref_benchmark_decode", path)
+    bd = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bd)
+    hidden, inter, heads, vocab, k, layers, max_seq = 256, 1000, 4, 211, 200, 2, 32
+    bd.HIDDEN, bd.INTERMEDIATE, bd.NUM_HEADS, bd.VOCAB_SIZE = hidden, inter, heads, vocab
+    for kind in ("dense", "global_moc"):
+        bd.ROW_SPECS[kind]["k"] = k
+    bd.ROW_SPECS["global_moc"]["ffn_mode"] = "masked_reference"      # the CPU-runnable definition of the same row
+    store = {}
+    for key, val in dict(hidden=hidden, inter=inter, heads=heads, vocab=vocab, k=k, layers=layers, max_seq=max_seq).items():
+        store["meta." + key] = np.int64(val)
+    gen = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, vocab, (1, 8), generator=torch.Generator().manual_seed(12))
+    store["prompt"] = prompt.numpy()
+    steps = 6
+    state = None
+    for kind in ("dense", "global_moc"):
+        torch.manual_seed(0)
+        model = bd.DecoderModel(layers, kind, "cpu", torch.bfloat16, max_seq).to(torch.bfloat16).eval()
+        if state is None:
+            with torch.no_grad():
+                for p_ in model.parameters():      # matrices ~N(0, 0.05) from seed 11, norm weights stay 1
+                    if p_.dim() > 1:
+                        p_.copy_(torch.randn(p_.shape, generator=gen) * 0.05)
+            state = {k_: v.detach().clone() for k_, v in model.state_dict().items()}
+            # the weights are not stored: decoder_weights() below rebuilds them from the seed in this order
+            store["state_names"] = np.array([k_ for k_, v in model.named_parameters() if v.dim() > 1])
+            store["state_shapes"] = np.array([list(v.shape) for _, v in model.named_parameters() if v.dim() > 1])
+        model.load_state_dict(state)
+        model.allocate_cache("cpu", torch.bfloat16)
+        rec = TopkRecorder(canonical=True)
+        with torch.no_grad(), mock.patch("torch.topk", rec):
+            logits = model.forward_prompt(prompt)[:, -1]
+            tokens, all_logits = [], [logits]
+            cur = logits.argmax(dim=-1, keepdim=True)
+            for i in range(steps):
+                tokens.append(cur)
+                logits = model.forward_step_static(cur, torch.tensor(prompt.shape[1] + i))[:, -1]
+                all_logits.append(logits)
+                cur = logits.argmax(dim=-1, keepdim=True)
+        put(store, f"{kind}.logits", torch.stack(all_logits, dim=1))      # [1, steps + 1, vocab]
+        store[f"{kind}.tokens"] = torch.cat(tokens, dim=1).numpy()            # [1, steps]: inputs of the decode steps
+    np.savez_compressed(HERE / "decoder_tiny_bf16.npz", **store)
+    print("wrote decoder_tiny_bf16")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of xiaohuangji/MoC")
+    ap.add_argument("--only", default="", help="comma-separated subset: tiny,cfg1,decode,decoder,host (default: all)")
     args = ap.parse_args()
+    only = set(filter(None, args.only.split(",")))
     sys.path.insert(0, args.reference)
     import moc.ffn as ref_ffn  # the reference's own module
     import moc.inference.inference_ffn as ref_inf
 
     torch.set_num_threads(1)   # fixed reduction order
-    gen_tiny(ref_ffn, torch.float32, "tiny_fp32")
-    gen_tiny(ref_ffn, torch.bfloat16, "tiny_bf16")
-    gen_cfg1(ref_ffn)
-    gen_decode(ref_inf, torch.float32, "decode_fp32")
-    gen_decode(ref_inf, torch.bfloat16, "decode_bf16")
-    import moc.config as ref_config
-    import moc.model as ref_model
-    gen_host(ref_model, ref_config)
+    if not only or "tiny" in only:
+        gen_tiny(ref_ffn, torch.float32, "tiny_fp32")
+        gen_tiny(ref_ffn, torch.bfloat16, "tiny_bf16")
+    if not only or "cfg1" in only:
+        gen_cfg1(ref_ffn)
+    if not only or "decode" in only:
+        gen_decode(ref_inf, torch.float32, "decode_fp32")
+        gen_decode(ref_inf, torch.bfloat16, "decode_bf16")
+    if not only or "decoder" in only:
+        gen_decoder(args.reference)
+    if not only or "host" in only:
+        import moc.config as ref_config
+        import moc.model as ref_model
+        gen_host(ref_model, ref_config)
 
 
 if __name__ == "__main__":
