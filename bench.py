@@ -51,9 +51,14 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=TOKENS, help="tokens per GPU (default: the configs[1] batch)")
     ap.add_argument("--dump-kernels", action="store_true", help="print per-launch durations of the last step")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="ffn", choices=["ffn", "train_130m", "decode_1b", "memory"],
+    ap.add_argument("--workload", default="ffn", choices=["ffn", "train_130m", "decode_1b", "memory", "decode_ffn"],
                     help="ffn: the headline single-layer benchmark (default). train_130m / decode_1b: the end-to-end "
                          "rows (whole LLaMA-style model around the FFN plugin, moc_b200.host), one JSON line each")
+    ap.add_argument("--batch", type=int, default=1, help="decode_ffn: token rows per call")
+    ap.add_argument("--decode-kind", default="global_moc", choices=["global_moc", "moc_2of8", "dense"],
+                    help="decode_ffn: which decode row")
+    ap.add_argument("--weight-sets", type=int, default=4,
+                    help="decode_ffn: distinct weight sets cycled through (4 x 67 MB: beyond the 126 MB L2)")
     ap.add_argument("--overlap", type=int, default=-1,
                     help="N>1: 1 = start the gradient all-reduce beside the dX GEMM, 0 = after the backward pass, "
                          "-1 (default) = beside the GEMM on 2 GPUs only: on 4 and 8 GPUs the overlapped collective "
@@ -916,6 +921,45 @@ def run_decode_1b(args, rank, world, local_rank):
     }), flush=True)
 
 
+def run_decode_ffn(args):
+    """One decode row of BASELINE config 3 as plain stream launches (no CUDA graph): `--steps` calls of the decode
+    FFN at `--batch` rows, cycling through `--weight-sets` distinct weight sets so that the weights come from HBM.
+    A small case for profilers and for quick timing; the graph-replayed figures of the headline line come from
+    bench_decode()."""
+    import torch
+
+    from moc_b200.inference import InferenceMoCSwiGLUFFN
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    grouped = args.decode_kind == "moc_2of8"
+    k = (D_FFN // 8) * 2 + min(2, D_FFN % 8) if grouped else K_SEL
+    mods = []
+    for _ in range(args.weight_sets):
+        m = InferenceMoCSwiGLUFFN(D, D_FFN, k, *((2, 8) if grouped else (None, None))).to(device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            for p in m.parameters():
+                p.copy_(torch.randn(p.shape, device=dev, generator=gen) * 0.02)
+        m.freeze_for_compile()
+        mods.append(m)
+    mode = "dense_baseline" if args.decode_kind == "dense" else "auto"
+    x = torch.randn(args.batch, D, device=dev, dtype=torch.bfloat16, generator=gen)
+    for i in range(args.warmup):
+        mods[i % len(mods)](x, mode=mode)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        y = mods[i % len(mods)](x, mode=mode)
+    e1.record()
+    torch.cuda.synchronize()
+    us = 1e3 * e0.elapsed_time(e1) / max(1, args.steps)
+    print(json.dumps({"workload": "decode_ffn", "kind": args.decode_kind, "batch": args.batch, "steps": args.steps,
+                      "warmup": args.warmup, "weight_sets": args.weight_sets, "us_per_call_stream_launches": us,
+                      "finite": bool(torch.isfinite(y.float()).all())}))
+
+
 def run_memory(args, rank, world, local_rank):
     """Peak training memory with the reference's protocol (benchmarks/memory/benchmark_memory.py:79-92: one warm-up
     step, reset_peak_memory_stats, one step, max_memory_allocated) for dense / moc / moc_gcp, on the 130m and 1b
@@ -1021,6 +1065,9 @@ def main():
         return
     if args.workload == "memory":
         run_memory(args, rank, world, local_rank)
+        return
+    if args.workload == "decode_ffn":
+        run_decode_ffn(args)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -216,8 +216,8 @@ def gen_host(ref_model, ref_config):
 def gen_decoder(reference_dir):
     """The reference's static-cache decoder (benchmarks/inference/benchmark_decode.py:312-362: DecoderModel with
     forward_prompt / forward_step_static) on a tiny configuration, bf16, CPU, with its FFNs evaluated by their
-    dense-masking definition (masked_reference, canonical tie rule): state_dict, prompt, and the logits and greedy
-    token of every decode step, for moc_b200.host.GreedyDecoder. Row kinds: dense and global_moc."""
+    dense-masking definition (masked_reference, canonical tie rule): state_dict, prompt, the logits and greedy
+    token of every decode step and the channel set of every FFN call, for moc_b200.host.GreedyDecoder. Row kinds: dense and global_moc."""
     import importlib.util
 
     path = Path(reference_dir) / "benchmarks" / "inference" / "benchmark_decode.py"
@@ -262,6 +262,10 @@ def gen_decoder(reference_dir):
                 all_logits.append(logits)
                 cur = logits.argmax(dim=-1, keepdim=True)
         put(store, f"{kind}.logits", torch.stack(all_logits, dim=1))      # [1, steps + 1, vocab]
+        # the channel sets the reference selected, in call order (prompt pass: one call per layer over the prompt
+        # rows; then one call per layer and decode step), each sorted by channel
+        for c, (_, _, idx) in enumerate(rec.calls):
+            store[f"{kind}.idx.{c}"] = idx.sort(dim=-1).values.to(torch.int16).numpy()
         store[f"{kind}.tokens"] = torch.cat(tokens, dim=1).numpy()            # [1, steps]: inputs of the decode steps
     np.savez_compressed(HERE / "decoder_tiny_bf16.npz", **store)
     print("wrote decoder_tiny_bf16")
