@@ -222,7 +222,7 @@ int moc_ffn_fwd(int dtype, int select, int64_t tokens, int64_t d, int64_t d_ffn,
   // channel selection on the rounded G (moc/ffn.py:144-147); the same kernel gathers the selected channels of U
   // into the compact saved set and turns the G rows into Z' = mask * round(round(SiLU(G)) * U) in place
   // (moc/ffn.py:156-161, :166-169)
-  SelectFuse fuse{u_dense, u_sel, s_sel, z_sel};
+  SelectFuse fuse{u_dense, u_sel, s_sel, z_sel, status};
   if (select == MOC_SELECT_POST_SILU_ABS) {
     // Top-K on |SiLU(G)| (moc/ffn.py:336-339): scores in a third scratch matrix, plain selection on them (the
     // g_sel array receives scores first), then g, u of the chosen channels are gathered from the dense rows and

@@ -69,7 +69,12 @@ struct SelectFuse {
   void* u_sel;
   void* s_sel;   // may be null
   void* z_sel;   // may be null
+  int* status;   // device status word for kernels with bounded waits; null: only kernels without waits are used
 };
+// Persistent shared-memory-staged form of the fused Top-K launch for bf16 rows (select_stream.cu)
+bool select_stream_supported(int64_t ldg, int d_ffn, int k, const void* g, const void* u_dense);
+int launch_select_stream(void* g, int64_t ldg, int tokens, int d_ffn, int k, const SelectFuse& fuse, int16_t* idx,
+                         void* g_sel, uint32_t* bitmap, uint16_t* rank0, int* status, cudaStream_t stream);
 int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, int k, const SelectFuse* fuse,
                        int16_t* idx, void* g_sel, uint32_t* bitmap, uint16_t* rank0, cudaStream_t stream);
 int launch_select_2of8(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, const SelectFuse* fuse, int16_t* idx,

@@ -98,6 +98,20 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
                : "memory");
 }
 
+// Untiled bulk copy shared -> global, tracked by the bulk async-group of the issuing thread; both addresses
+// 16-byte aligned, size a multiple of 16. Shared-memory writes made with ordinary stores must be ordered
+// before it by fence_proxy_async_smem() in the writing threads and a barrier.
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// every committed bulk store of this thread has finished READING its shared-memory source
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// every committed bulk store of this thread is complete
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- warp-level MMA (m16n8k16, bf16 in, fp32 accumulate) for products with very few columns ------------
 // Four 8x8 b16 matrices from shared memory; lanes 8i..8i+7 give the row addresses of matrix i, register i
 // receives matrix i (thread (g, t) = (lane / 4, lane % 4) holds elements [g][2t], [g][2t + 1]).
