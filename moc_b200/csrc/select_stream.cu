@@ -62,6 +62,7 @@ struct RowSelShared {
   uint64_t full[2];
   uint32_t wtot[2][8];     // warp totals of the block scan of pass 4, double-buffered over chunks
   uint32_t stot[8];        // warp totals of the block scan of pass 2
+  uint32_t has_top;        // the row holds +inf or a positive NaN
   uint32_t bin_pos;        // position of the threshold bin in key order, counted from the top
   uint32_t k_rem;          // rank of the K-th key inside that bin, counted from the top
   int abort;
@@ -77,6 +78,19 @@ __device__ __forceinline__ uint32_t rs_incl_scan(uint32_t v, int lane) {
     if (lane >= o) v += nb;
   }
   return v;
+}
+
+// bits 0..15 -> even positions, bits 16..31 -> odd positions (outer perfect shuffle)
+__device__ __forceinline__ uint32_t rs_interleave16(uint32_t x) {
+  uint32_t t = (x ^ (x >> 8)) & 0x0000FF00u;
+  x = x ^ t ^ (t << 8);
+  t = (x ^ (x >> 4)) & 0x00F000F0u;
+  x = x ^ t ^ (t << 4);
+  t = (x ^ (x >> 2)) & 0x0C0C0C0Cu;
+  x = x ^ t ^ (t << 2);
+  t = (x ^ (x >> 1)) & 0x22222222u;
+  x = x ^ t ^ (t << 1);
+  return x;
 }
 
 // raw bin (upper 11 bits of the bf16 pattern) at position i of the key order, counted from the largest key:
@@ -213,6 +227,8 @@ __global__ void __launch_bounds__(kRsThreads, kRsMaxCtasPerSm) select_stream_ker
         c[j] = p0 + j < kRsBins ? sh.hist[rs_raw_bin(p0 + j)] : 0u;
         local += c[j];
       }
+      // positions 0..3 are the raw bins of +inf and the positive NaNs
+      if (tid == 0) sh.has_top = c[0] | c[1] | c[2] | c[3];
       const uint32_t incl = rs_incl_scan(local, lane);
       if (lane == 31) sh.stot[warp] = incl;
       rs_compute_sync();
@@ -278,8 +294,12 @@ __global__ void __launch_bounds__(kRsThreads, kRsMaxCtasPerSm) select_stream_ker
     uint32_t* bm_row = a.bitmap + static_cast<int64_t>(row) * a.words;
     uint16_t* rk_row = a.rank0 + static_cast<int64_t>(row) * a.words;
     const uint32_t thr_key = order_key16(static_cast<uint16_t>(raw_thr));
-    // a positive threshold orders raw patterns like signed 16-bit integers (every negative value lies below it)
-    const int32_t thr_hi = static_cast<int32_t>((raw_thr << 16) | 0xFFFFu), thr_lo = static_cast<int32_t>(raw_thr << 16);
+    // Packed bf16 compares order the row like the keys do when the threshold is a positive normal number and the
+    // row holds neither +inf nor a positive NaN (a NaN compares false but has the largest key; -0 equals +0 but
+    // has a smaller key): every negative pattern then lies below the threshold under both orders.
+    const bool packed_cmp = positive && raw_thr >= 0x0080u && sh.has_top == 0u;
+    const uint32_t thr_pair = raw_thr * 0x00010001u;
+    const __nv_bfloat162 thr2 = *reinterpret_cast<const __nv_bfloat162*>(&thr_pair);
     int chunk = 0;
 #pragma unroll 1
     for (int w0 = 0; w0 < a.words; w0 += kRsCompute, ++chunk) {
@@ -292,16 +312,18 @@ __global__ void __launch_bounds__(kRsThreads, kRsMaxCtasPerSm) select_stream_ker
           const int v = (v0 + (tid >> 1)) & 3;   // rotated start: the 64-byte stride of the words meets no bank twice
           const uint4 q = g4[v];
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-          uint32_t gt8 = 0, eq8 = 0;
-          if (positive) {
+          if (packed_cmp) {
+            // two channels per compare instruction; flags in split order: even channels in bits 0..15, odd
+            // channels in bits 16..31 (pair 4 v + j -> bits 4 v + j and 16 + 4 v + j)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              gt8 |= (static_cast<int32_t>(w[j] << 16) > thr_lo ? 1u : 0u) << (2 * j);
-              gt8 |= (static_cast<int32_t>(w[j]) > thr_hi ? 1u : 0u) << (2 * j + 1);
-              eq8 |= ((w[j] & 0xFFFFu) == raw_thr ? 1u : 0u) << (2 * j);
-              eq8 |= ((w[j] >> 16) == raw_thr ? 1u : 0u) << (2 * j + 1);
+              const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+              const uint32_t sel = 0x00010001u << (4 * v + j);
+              gtm |= __hgt2_mask(h, thr2) & sel;
+              eqm |= __hge2_mask(h, thr2) & sel;     // greater or equal; reduced to equal below
             }
           } else {
+            uint32_t gt8 = 0, eq8 = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint32_t m = (w[j] >> 15) & 0x00010001u;
@@ -312,9 +334,14 @@ __global__ void __launch_bounds__(kRsThreads, kRsMaxCtasPerSm) select_stream_ker
               eq8 |= (lo == thr_key ? 1u : 0u) << (2 * j);
               eq8 |= (hi == thr_key ? 1u : 0u) << (2 * j + 1);
             }
+            gtm |= gt8 << (8 * v);
+            eqm |= eq8 << (8 * v);
           }
-          gtm |= gt8 << (8 * v);
-          eqm |= eq8 << (8 * v);
+        }
+        if (packed_cmp) {
+          eqm &= ~gtm;
+          gtm = rs_interleave16(gtm);
+          if (eqm) eqm = rs_interleave16(eqm);
         }
       }
       // block scan over (greater, equal) counts, packed 16 + 16 bits

@@ -214,3 +214,47 @@ def test_fused_forward_selection_bit_exact(tokens, d_ffn, k, save_sz):
         assert torch.equal(bits(z_sel.cpu()), bits(z_got.to(torch.bfloat16)))
         s_ulp = torch.maximum(s_ref.abs(), torch.tensor(1e-37)) * 2.0 ** -7
         assert bool(((s_sel.cpu().float() - s_ref).abs() <= s_ulp).all())
+
+
+@pytest.mark.parametrize("k", [40, 700])
+def test_fused_forward_selection_with_inf_and_nan(k):
+    """Rows with +inf, -inf and NaN through the fused selection of moc_ffn_fwd (every token row is the same one-hot
+    vector and the other columns of W_gate are zero, so no 0 * inf arises): NaN counts as the largest value and
+    +inf comes next, as in torch.topk and the oracle's key order. The packed floating-point compares of the kernel's
+    fast path are not valid for such rows; this checks that it steps aside."""
+    from moc_b200 import ffn as F
+
+    lib = _lib.lib()
+    dev = torch.device("cuda")
+    tokens, d, d_ffn = 1030, 64, 1376
+    gen = torch.Generator().manual_seed(5)
+    g_row = (torch.randn(d_ffn, generator=gen) * 0.9).to(torch.bfloat16)
+    g_row[[3, 500, 1375]] = float("inf")
+    g_row[[4, 77]] = float("-inf")
+    g_row[[9, 640, 1001]] = float("nan")
+    wg = torch.zeros(d_ffn, d, dtype=torch.bfloat16)
+    wg[:, 0] = g_row
+    wu = (torch.randn(d_ffn, d, generator=gen) * 0.5).to(torch.bfloat16)
+    wdt = (torch.randn(d_ffn, d, generator=gen) * 0.02).to(torch.bfloat16)
+    x = torch.zeros(tokens, d, dtype=torch.bfloat16)
+    x[:, 0] = 1.0
+    words = lib.moc_mask_words(d_ffn)
+    y = torch.empty(tokens, d, device=dev, dtype=torch.bfloat16)
+    idx = torch.full((tokens, k), -1, device=dev, dtype=torch.int16)
+    g_sel = torch.zeros(tokens, k, device=dev, dtype=torch.bfloat16)
+    u_sel = torch.zeros_like(g_sel)
+    bitmap = torch.zeros(tokens, words, device=dev, dtype=torch.int32)
+    rank0 = torch.zeros(tokens, words, device=dev, dtype=torch.int16)
+    ws_bytes = lib.moc_ffn_fwd_workspace_bytes(0, tokens, d_ffn)
+    ws = torch.zeros(ws_bytes, device=dev, dtype=torch.uint8)
+    rc = F._call_fwd(lib, 0, 0, tokens, d, d_ffn, k, x.to(dev), wg.to(dev), wu.to(dev), wdt.to(dev), y, idx, g_sel, u_sel,
+                     None, None, bitmap, rank0, ws, ws_bytes, dev)
+    _lib.check(rc, "moc_ffn_fwd")
+    _lib.check(lib.moc_read_status(ws.data_ptr(), _lib.stream_ptr()), "device status")
+    torch.cuda.synchronize()
+    _, ref_idx = O.canonical_topk(g_row[None, :], k)
+    assert torch.equal(idx.cpu().to(torch.int64), ref_idx.expand(tokens, k))
+    for ch in (3, 500, 1375, 9, 640, 1001):
+        assert ch in ref_idx[0].tolist()
+    ref_bm = O.selection_bitmap(ref_idx, d_ffn)
+    assert np.array_equal(bitmap.cpu().numpy().view(np.uint32), np.repeat(ref_bm, tokens, axis=0))
