@@ -236,6 +236,27 @@ int64_t moc_side_launch_count(void);
  * Process-wide. No counterpart in the reference (it has no distributed code). */
 int moc_set_overlap_sm_reserve(int sms);
 
+/* Data-parallel training: in-place sum (average != 0: mean) over `world` ranks (<= 8, one process per GPU of one
+ * node) of a gradient buffer that every rank holds in a symmetric allocation mapped by its peers. The
+ * north star asks for the weight gradients to be all-reduced over NVLink; the reference itself has no distributed
+ * code, so this entry point has no counterpart there.
+ *   peer_buffers[r], peer_flags[r] (HOST arrays of `world` device pointers): rank r's buffer and flag words as
+ *   mapped in this process; entry `rank` is the local one. Flags: moc_symm_allreduce_flag_bytes() bytes per rank,
+ *   zeroed once when the allocation is made, never touched by the caller afterwards.
+ *   multicast_buffer: multicast address of the buffer (NVSwitch; the kernel then reduces in the switch with
+ *   multimem.ld_reduce / multimem.st), or NULL: plain peer loads and stores.
+ *   bytes: size of the buffer, a multiple of 16. call: 1, 2, 3, ... - the same sequence on every rank.
+ *   ctas: CTAs of 512 threads to launch (a few per SM that the caller wants the reduction to occupy).
+ * Every rank must make the same sequence of calls. Rank r reduces the r-th slice of the buffer and writes it to
+ * all ranks; ranks meet before the first read and after the last write, with bounded waits (about one second):
+ * after a time-out the buffer's contents are unspecified and moc_symm_allreduce_status reports
+ * MOC_ERR_DEVICE_TIMEOUT. The library allocates nothing and knows nothing about how the mapping was made. */
+int moc_symm_allreduce(int dtype, int rank, int world, void* const* peer_buffers, void* multicast_buffer,
+                       void* const* peer_flags, int64_t bytes, int average, uint32_t call, int ctas, void* stream);
+int64_t moc_symm_allreduce_flag_bytes(void);
+/* Synchronises `stream`, then MOC_OK or MOC_ERR_DEVICE_TIMEOUT for the local flag words `flags`. */
+int moc_symm_allreduce_status(const void* flags, void* stream);
+
 /* Synchronises `stream` and returns MOC_OK, or MOC_ERR_DEVICE_TIMEOUT if a kernel of the
  * last call that used `workspace` recorded a bounded-wait failure in its status area. */
 int moc_read_status(const void* workspace, void* stream);

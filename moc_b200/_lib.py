@@ -41,6 +41,9 @@ SIGNATURES = {
     "moc_profile_end": (c_int, [_P, c_int]),
     "moc_side_launch_count": (c_int64, []),
     "moc_set_overlap_sm_reserve": (c_int, [c_int]),
+    "moc_symm_allreduce": (c_int, [c_int, c_int, c_int, _P, _P, _P, c_int64, c_int, ctypes.c_uint32, c_int, _P]),
+    "moc_symm_allreduce_flag_bytes": (c_int64, []),
+    "moc_symm_allreduce_status": (c_int, [_P, _P]),
     "moc_read_status": (c_int, [_P, _P]),
     "moc_publish_status": (c_int, [_P, _P, _P]),
     "moc_debug_set_wait_cycles": (c_int, [c_int64]),

@@ -102,7 +102,8 @@ def moc_ffn_backward(grad_y2d, x2d, gate_w, up_w, down_w_t, idx, g_sel, u_sel, s
     dx = torch.empty(tokens, d, device=dev, dtype=dt)
     # the three weight gradients are views of one buffer, so that a data-parallel caller can reduce them with a
     # single collective (moc_b200.dp)
-    bucket = torch.empty(3, d_ffn * d, device=dev, dtype=dt)
+    bucket = _bucket_provider(gate_w.data_ptr(), 3 * d_ffn * d, dt, dev) if _bucket_provider is not None else None
+    bucket = torch.empty(3, d_ffn * d, device=dev, dtype=dt) if bucket is None else bucket.view(3, d_ffn * d)
     d_down = bucket[0].view(d, d_ffn)
     d_gate = bucket[1].view(d_ffn, d)
     d_up = bucket[2].view(d_ffn, d)
@@ -157,6 +158,18 @@ _grad_ready_hook = None
 # collective that takes SMs away only makes it proportionally slower; for the collective to find free SMs while
 # the GEMM runs, the caller also reserves some (moc_set_overlap_sm_reserve, see moc_b200.dp.GradAllReducer).
 _grad_ready_early = False
+
+
+# Optional source of the [3 * d_ffn * d] gradient buffer of a backward call: provider(key, numel, dtype, device) ->
+# flat tensor or None (None: a fresh allocation). `key` identifies the layer (address of its gate weight). A data-
+# parallel reducer that needs the gradients in memory its peers can reach hands out its own buffers here
+# (moc_b200.dp.SymmGradReducer).
+_bucket_provider = None
+
+
+def set_bucket_provider(provider) -> None:
+    global _bucket_provider
+    _bucket_provider = provider
 
 
 def set_grad_ready_hook(hook, early: bool = False) -> None:
