@@ -65,6 +65,10 @@ def parse_args():
                          "was faster in most runs (8 GPUs, 32 SMs reserved: 3.06-3.18 against 3.34 ms per step) but "
                          "single runs took 4-5 ms when its CTAs did not all fit the reserved SMs")
     ap.add_argument("--reserve-sms", type=int, default=16, help="N>1 with --overlap: SMs the dX GEMM leaves free")
+    ap.add_argument("--reduce", default="symm", choices=["symm", "nccl"],
+                    help="N>1: symm = the library's own all-reduce kernel over symmetric NVLink memory, started beside "
+                         "the dX GEMM (falls back to nccl, on every rank, if the symmetric allocation cannot be set "
+                         "up); nccl = one NCCL all-reduce of the gradient bucket")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N>1: cap on the CTAs of an NCCL kernel (0: NCCL default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode FFN micro-benchmark (N=1 only)")
@@ -75,15 +79,15 @@ def parse_args():
 
 
 def workload_config(args, world):
-    overlap = args.overlap if args.overlap >= 0 else (1 if world == 2 else 0)
     return {
         "workload": f"configs[1]: single MoC FFN layer fwd+bwd, 1b preset d={D} d_ffn={D_FFN} K={K_SEL}, "
                     f"X[8,2048,{D}] bf16, ffn_type={args.ffn_type}",
         "tokens_per_gpu": args.tokens,
         "global_tokens": args.tokens * world,
-        "parallelism": (f"token-sharded dp{world}, one NCCL all-reduce of the three weight gradients per step"
-                        + (f", started beside the dX GEMM ({args.reserve_sms} SMs reserved)" if overlap else
-                           ", after the backward pass")) if world > 1 else "single GPU",
+        # how the gradients are reduced (own NVLink kernel or NCCL, beside the dX GEMM or after it) is reported in the
+        # line's "reduce" key: it can change at run time (fallback), and both arms must print the same config
+        "parallelism": (f"token-sharded dp{world}, the three weight gradients averaged over NVLink once per step"
+                        if world > 1 else "single GPU"),
         "l2": "inputs larger than L2: every step streams >600 MB of activations, weights and scratch "
               "(126 MB L2), no explicit flush",
     }
@@ -518,17 +522,26 @@ def run_ours(args, rank, world, local_rank):
     dy_host = torch.randn(8, tokens // 8, D, generator=gx).bfloat16().pin_memory()
     x = x_host.to(dev).requires_grad_(True)
     dy = dy_host.to(dev)
-    if args.overlap < 0:
-        args.overlap = 1 if world == 2 else 0
-    reducer = (GradAllReducer(average=True, overlap=bool(args.overlap), reserve_sms=args.reserve_sms)
-               if world > 1 else None)
+    reducers = {"r": None}
+    reduce_note = None
+    if world > 1:
+        from moc_b200.dp import SymmGradReducer
+        if args.reduce == "symm":
+            # the own kernel has a fixed CTA count, so it always fits beside the dX GEMM: overlap at every N
+            overlap = True if args.overlap < 0 else bool(args.overlap)
+            reducers["r"] = SymmGradReducer(average=True, overlap=overlap, reserve_sms=args.reserve_sms)
+            args.overlap = int(overlap)
+        else:
+            if args.overlap < 0:
+                args.overlap = 1 if world == 2 else 0
+            reducers["r"] = GradAllReducer(average=True, overlap=bool(args.overlap), reserve_sms=args.reserve_sms)
 
     def step(xin, dyin):
         module.zero_grad(set_to_none=True)
         xin.grad = None
         y = module(xin)
-        if reducer is not None:
-            with reducer:
+        if reducers["r"] is not None:
+            with reducers["r"]:
                 y.backward(dyin)
         else:
             y.backward(dyin)
@@ -540,7 +553,32 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     moc_b200.set_status_checks(True)    # one checked step: raises if a device-side wait timed out
-    step(x, dy)
+    if world > 1 and args.reduce == "symm":
+        # the first step sets up the symmetric gradient buffers; if that fails on any rank, every rank goes back
+        # to the NCCL all-reduce
+        failed, why = 0, ""
+        try:
+            step(x, dy)
+            reducers["r"].check()
+        except Exception as exc:      # noqa: BLE001 - any set-up failure selects the fallback
+            failed, why = 1, f"{type(exc).__name__}: {exc}"
+        flag = torch.tensor([failed], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()):
+            reduce_note = "nccl (symmetric-memory reducer unavailable" + (f": {why[:200]}" if why else " on another rank") + ")"
+            moc_b200.ffn.set_grad_ready_hook(None)
+            moc_b200.ffn.set_bucket_provider(None)
+            lib.moc_set_overlap_sm_reserve(0)
+            args.reduce = "nccl"
+            args.overlap = 1 if world == 2 else 0
+            reducers["r"] = GradAllReducer(average=True, overlap=bool(args.overlap), reserve_sms=args.reserve_sms)
+            step(x, dy)
+        else:
+            reduce_note = ("own kernel over symmetric memory, " +
+                           ("in-switch reduction (multimem)" if reducers["r"].multicast else "peer loads and stores") +
+                           f", {reducers['r'].ctas} CTAs")
+    else:
+        step(x, dy)
     moc_b200.set_status_checks(False)
     dp_check = None
     if world > 1:
@@ -811,6 +849,9 @@ def run_ours(args, rank, world, local_rank):
             "host_wall_ms_per_step": 1e3 * wall / args.steps, "k_selected": k_eff, "decode": decode,
             "strong": strong, "sustained": sustained, "variants": variants, "reference_gpu": reference_gpu,
             "dp_check": dp_check,
+            "reduce": ((reduce_note or "one NCCL all-reduce of the gradient bucket") +
+                       (f", started beside the dX GEMM ({args.reserve_sms} SMs reserved)" if args.overlap else
+                        ", after the backward pass")) if world > 1 else None,
         }
         print(json.dumps(out), flush=True)
     if world > 1:
