@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=1, help="decode_ffn: token rows per call")
     ap.add_argument("--decode-kind", default="global_moc", choices=["global_moc", "moc_2of8", "dense"],
                     help="decode_ffn: which decode row")
+    ap.add_argument("--graph", action="store_true",
+                    help="decode_ffn: time replays of one CUDA graph that holds one call per weight set")
     ap.add_argument("--weight-sets", type=int, default=4,
                     help="decode_ffn: distinct weight sets cycled through (4 x 67 MB: beyond the 126 MB L2)")
     ap.add_argument("--overlap", type=int, default=-1,
@@ -64,7 +66,9 @@ def parse_args():
                          "-1 (default) = beside the GEMM on 2 GPUs only: on 4 and 8 GPUs the overlapped collective "
                          "was faster in most runs (8 GPUs, 32 SMs reserved: 3.06-3.18 against 3.34 ms per step) but "
                          "single runs took 4-5 ms when its CTAs did not all fit the reserved SMs")
-    ap.add_argument("--reserve-sms", type=int, default=16, help="N>1 with --overlap: SMs the dX GEMM leaves free")
+    ap.add_argument("--reserve-sms", type=int, default=-1,
+                    help="N>1 with --overlap: SMs the dX GEMM leaves free (default: 8 for the own kernel - measured on "
+                         "4 GPUs: 2.866 / 2.853 / 2.885 / 2.931 ms per step with 4 / 8 / 16 / 24 SMs - and 16 for NCCL)")
     ap.add_argument("--reduce", default="symm", choices=["symm", "nccl"],
                     help="N>1: symm = the library's own all-reduce kernel over symmetric NVLink memory, started beside "
                          "the dX GEMM (falls back to nccl, on every rank, if the symmetric allocation cannot be set "
@@ -526,6 +530,8 @@ def run_ours(args, rank, world, local_rank):
     reduce_note = None
     if world > 1:
         from moc_b200.dp import SymmGradReducer
+        if args.reserve_sms < 0:
+            args.reserve_sms = 8 if args.reduce == "symm" else 16
         if args.reduce == "symm":
             # the own kernel has a fixed CTA count, so it always fits beside the dX GEMM: overlap at every N
             overlap = True if args.overlap < 0 else bool(args.overlap)
@@ -570,6 +576,7 @@ def run_ours(args, rank, world, local_rank):
             moc_b200.ffn.set_bucket_provider(None)
             lib.moc_set_overlap_sm_reserve(0)
             args.reduce = "nccl"
+            args.reserve_sms = 16
             args.overlap = 1 if world == 2 else 0
             reducers["r"] = GradAllReducer(average=True, overlap=bool(args.overlap), reserve_sms=args.reserve_sms)
             step(x, dy)
@@ -996,9 +1003,31 @@ def run_decode_ffn(args):
     e1.record()
     torch.cuda.synchronize()
     us = 1e3 * e0.elapsed_time(e1) / max(1, args.steps)
-    print(json.dumps({"workload": "decode_ffn", "kind": args.decode_kind, "batch": args.batch, "steps": args.steps,
-                      "warmup": args.warmup, "weight_sets": args.weight_sets, "us_per_call_stream_launches": us,
-                      "finite": bool(torch.isfinite(y.float()).all())}))
+    out = {"workload": "decode_ffn", "kind": args.decode_kind, "batch": args.batch, "steps": args.steps,
+           "warmup": args.warmup, "weight_sets": args.weight_sets, "us_per_call_stream_launches": us,
+           "finite": bool(torch.isfinite(y.float()).all())}
+    if args.graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for m in mods:
+                m(x, mode=mode)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for m in mods:
+                m(x, mode=mode)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        reps = max(1, args.steps // len(mods))
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        out["us_per_call_graph"] = 1e3 * e0.elapsed_time(e1) / (reps * len(mods))
+    print(json.dumps(out))
 
 
 def run_memory(args, rank, world, local_rank):

@@ -370,6 +370,8 @@ struct DecodeWs {
 // 8 rows) and from 8 rows for the dense baseline (47 against 68 us)
 constexpr int kDecodeGemmMinBatch = 16;
 constexpr int kDenseGemmMinBatch = 8;
+// from this many rows on (beyond the persistent launch): grouped full-K gate + up launch, fused selection, split-K down
+constexpr int kWideMinBatch = 9;
 
 // fp32 bytes of the split-K partial blocks of one skinny product over `rows` weight rows: splits * tiles of 128
 // rows <= SM count while the tiles fit the SMs, one block of round_up(rows, 128) rows (splits = 1) beyond that
@@ -512,6 +514,61 @@ static int down_dense(const bf16* z_dense, int64_t ld, const bf16* w_down_t, bf1
   return launch_skinny_consume<0>(partial, nullptr, splits, d, batch, y, d, d, nullptr, 0, nullptr, 0, stream);
 }
 
+// z = round(round(SiLU(g)) * u) over n8 vectors of 8 elements (dense baseline for more than 8 rows)
+__global__ void __launch_bounds__(256)
+decode_swiglu_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, uint4* __restrict__ z, int64_t n8) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float gv[8], uv[8];
+  unpack8(g[i], gv);
+  unpack8(u[i], uv);
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float s0, z0, s1, z1;
+    moc_fwd_point<bf16>(gv[2 * j], uv[2 * j], s0, z0);
+    moc_fwd_point<bf16>(gv[2 * j + 1], uv[2 * j + 1], s1, z1);
+    o[j] = (__float_as_uint(z0) >> 16) | (__float_as_uint(z1) & 0xFFFF0000u);   // both already bf16 values
+  }
+  z[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// G[b, f] = round(x[b] . W_gate[f]) and U[b, f] = round(x[b] . W_up[f]) for every channel, as ONE grouped launch of
+// the single-CTA tcgen05 kernel with the weights as the M operand (128-row tiles, full K, MMA N = batch rounded up
+// to 16) and a transposed store: each weight matrix is streamed once, no split-K partial blocks. Either weight may
+// be null (that product is skipped).
+static int gate_up_rows(const bf16* x, const bf16* w_gate, const bf16* w_up, bf16* g_out, bf16* u_out, int64_t ld,
+                        int batch, int d, int d_ffn, int* status, cudaStream_t stream) {
+  GemmProblem p = {};
+  p.dtype = kBF16;
+  p.impl = 3;
+  p.status = status;
+  p.m = d_ffn;
+  p.n = batch;
+  p.k0 = d;
+  p.epi.kind = kEpiStore;
+  int g = 0;
+  const bf16* w[2] = {w_gate, w_up};
+  bf16* out[2] = {g_out, u_out};
+  for (int i = 0; i < 2; ++i) {
+    if (!w[i]) continue;
+    p.a[g].ptr = w[i];
+    p.a[g].ld = d;
+    p.a[g].mn_major = 0;
+    p.b[g].ptr = x;
+    p.b[g].ld = d;
+    p.b[g].mn_major = 0;
+    p.epi.c[g] = out[i];
+    p.epi.ldc[g] = ld;
+    p.epi.transposed[g] = 1;
+    ++g;
+  }
+  if (g == 0) return kOk;
+  p.groups = g;
+  prof_mark(kProfDecodeGate, stream);
+  return launch_gemm(p, stream);
+}
+
 static int launch_down(const bf16* z, const int16_t* idx, const bf16* w_down_t, bf16* y, float* partial, int batch,
                        int k, int d, cudaStream_t stream) {
   const DownPlan p = plan_down(batch, d, k);
@@ -618,6 +675,31 @@ int decode_global(int64_t batch, int64_t d, int64_t d_ffn, int64_t k, int rule, 
   }
   if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
   const bf16* xb = static_cast<const bf16*>(x);
+  if (batch >= kWideMinBatch && aligned16(w_up, w_down_t, x) && (gate_scores || aligned16(w_gate, w_gate, w_gate))) {
+    // More than 8 rows: between them the rows select (nearly) every channel, so all three weight matrices are
+    // streamed once. Four launches: gate and up projections of every channel in one grouped tensor-core launch,
+    // the fused selection of the training forward (the score rows become the zero-filled Z' rows in place), the
+    // down projection as a split-K product over Z', and its fixed-order reduction.
+    const int64_t ld = ffn_ld(d_ffn);
+    if (gate_scores &&
+        cudaMemcpy2DAsync(w.gate, ld * 2, gate_scores, d_ffn * 2, d_ffn * 2, batch, cudaMemcpyDeviceToDevice, stream) !=
+            cudaSuccess)
+      return check_last("decode: copy of the caller's gate scores");
+    if ((rc = gate_up_rows(xb, gate_scores ? nullptr : static_cast<const bf16*>(w_gate), static_cast<const bf16*>(w_up),
+                           w.gate, w.u, ld, (int)batch, (int)d, (int)d_ffn, w.status, stream)) != kOk)
+      return rc;
+    SelectFuse fuse{w.u, w.z, nullptr, nullptr, w.status};   // u_sel lands in the z buffer; it is not used further
+    if (rule == 0)
+      rc = launch_topk_select(kBF16, w.gate, ld, (int)batch, (int)d_ffn, (int)k, &fuse, w.idx, w.g_sel, w.bitmap, w.rank0,
+                              stream);
+    else
+      rc = launch_select_2of8(kBF16, w.gate, ld, (int)batch, (int)d_ffn, &fuse, w.idx, w.g_sel, w.bitmap, w.rank0, stream);
+    if (rc != kOk) return rc;
+    rc = down_dense(w.gate, ld, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), (int)batch, (int)d,
+                    (int)d_ffn, w.status, w.partial, w.partial_set_bytes, stream);
+    prof_mark(kProfEnd, stream);
+    return rc;
+  }
   void* scores = w.gate;
   int64_t ld_scores = ffn_ld(d_ffn);
   if (gate_scores) {   // scores computed by the caller: contiguous [batch, d_ffn]
@@ -655,6 +737,22 @@ int decode_dense(int64_t batch, int64_t d, int64_t d_ffn, const void* x, const v
     return rc;
   }
   if (cudaMemsetAsync(w.status, 0, 256, stream) != cudaSuccess) return check_last("cudaMemsetAsync");
+  if (batch >= kWideMinBatch && aligned16(w_gate, w_up, w_down_t) && aligned16(x, x, x)) {
+    // gate and up of every channel in one grouped launch, SwiGLU elementwise, split-K down projection
+    const int64_t ld = ffn_ld(d_ffn);
+    if ((rc = gate_up_rows(static_cast<const bf16*>(x), static_cast<const bf16*>(w_gate), static_cast<const bf16*>(w_up),
+                           w.gate, w.u, ld, (int)batch, (int)d, (int)d_ffn, w.status, stream)) != kOk)
+      return rc;
+    const int64_t n8 = batch * ld / 8;
+    prof_mark(kProfDecodeDense, stream);
+    decode_swiglu_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(w.gate), reinterpret_cast<const uint4*>(w.u), reinterpret_cast<uint4*>(w.gate), n8);
+    if ((rc = check_last("decode_swiglu")) != kOk) return rc;
+    rc = down_dense(w.gate, ld, static_cast<const bf16*>(w_down_t), static_cast<bf16*>(y), (int)batch, (int)d,
+                    (int)d_ffn, w.status, w.partial, w.partial_set_bytes, stream);
+    prof_mark(kProfEnd, stream);
+    return rc;
+  }
   if (batch >= kDenseGemmMinBatch) {
     // three skinny tensor-core products; SwiGLU is applied while the gate and up partial blocks are reduced
     const int64_t ld = ffn_ld(d_ffn);

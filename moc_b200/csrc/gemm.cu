@@ -149,11 +149,13 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
   GemmMaps maps;
   memset(&maps, 0, sizeof(maps));
   const int nmaps = p.k1 > 0 ? 2 : p.groups;
+  // products with few columns (decode: N = batch rows): the MMA and the B tile are as narrow as N allows
+  const int mma_n = (!p.b[0].mn_major && p.n <= kBlockN / 2) ? (p.n + 15) / 16 * 16 : kBlockN;
   int rc;
   for (int i = 0; i < nmaps; ++i) {
     const int kext = (p.k1 > 0 && i == 1) ? p.k1 : p.k0;
     if ((rc = make_operand_map(&maps.a[i], p.a[i], p.m, kext, kBlockM)) != kOk) return rc;
-    if ((rc = make_operand_map(&maps.b[i], p.b[i], p.n, kext, kBlockN)) != kOk) return rc;
+    if ((rc = make_operand_map(&maps.b[i], p.b[i], p.n, kext, mma_n)) != kOk) return rc;
     if (p.a[i].mn_major != p.a[0].mn_major || p.b[i].mn_major != p.b[0].mn_major) {
       set_error("all K segments / groups of one launch must use the same operand majors");
       return kErrUnsupported;
@@ -172,6 +174,7 @@ static int launch_tcgen05(const GemmProblem& p, const Epi& epi, cudaStream_t str
   sh.status = p.status;
   sh.tile_counter = nullptr;
   sh.k_splits = p.k_splits > 1 ? p.k_splits : 1;
+  sh.mma_n = mma_n;
   if (sh.k_splits > 1 && (p.k1 > 0 || sh.k_splits > sh.kb0 ||
                           ceil_div_i(sh.kb0, sh.k_splits) * (sh.k_splits - 1) >= sh.kb0)) {
     set_error("split-K needs a single K segment and at least one k-block per split");
@@ -216,6 +219,7 @@ static int launch_tcgen05_pair(const GemmProblem& p, const Epi& epi, cudaStream_
   sh.status = p.status;
   sh.tile_counter = p.tile_counter;
   sh.k_splits = 1;
+  sh.mma_n = kBlockN;
   auto kern = gemm_tcgen05_pair_kernel<Epi>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
     return check_last("gemm pair smem attribute");

@@ -34,7 +34,8 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle span
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 4;          // ring depth with full-width (48 KiB) stages
+constexpr int kMaxStages = 8;       // ring depth with the narrow B tiles of products with few columns
 constexpr int kTileABytes = kBlockM * kBlockK * 2;   // 16 KiB
 constexpr int kTileBBytes = kBlockN * kBlockK * 2;   // 32 KiB
 constexpr int kStageBytes = kTileABytes + kTileBBytes;
@@ -63,6 +64,9 @@ struct GemmShape {
   int* tile_counter; // pair kernel only: zeroed device int; tiles are handed out in arrival order (null: round-robin)
   int k_splits;      // single-CTA kernel only: > 1 splits the k-blocks of segment 0 over that many tiles; the
                      // epilogue then sees group * k_splits + split as its group index (one partial result each)
+  int mma_n;         // single-CTA kernel only: N of the MMA instruction and rows of the B tile in shared memory;
+                     // kBlockN, or N rounded up to 16 for products with few columns (K-major B), whose MMAs would
+                     // otherwise spend most of their time on columns that do not exist
 };
 
 // Which problem, which K range and which output block a tile index stands for.
@@ -94,9 +98,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* full_bar = bars;                  // [kStages] TMA -> MMA
-  uint64_t* empty_bar = bars + kStages;       // [kStages] MMA -> TMA
-  uint64_t* tfull_bar = bars + 2 * kStages;   // [2] MMA -> epilogue
+  uint64_t* full_bar = bars;                     // [stages] TMA -> MMA
+  uint64_t* empty_bar = bars + kMaxStages;       // [stages] MMA -> TMA
+  uint64_t* tfull_bar = bars + 2 * kMaxStages;   // [2] MMA -> epilogue
+  static_assert((2 * kMaxStages + 4) * 8 + 8 <= 256, "barrier area overflow");
+  // a stage = the A tile + a B tile of mma_n rows; narrow B tiles leave room for a deeper ring, which a tile that
+  // streams its operand once from HBM needs to keep enough bytes in flight
+  const uint32_t stage_bytes = kTileABytes + static_cast<uint32_t>(sh.mma_n) * kBlockK * 2;
+  const int stages = min(kMaxStages, static_cast<int>((kStages * kStageBytes) / stage_bytes));
   uint64_t* tempty_bar = tfull_bar + 2;       // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -114,7 +123,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
       ptx::prefetch_tensormap(&maps.b[i]);
     }
 #pragma unroll
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kMaxStages; ++s) {
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
     }
@@ -138,7 +147,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const TileWork tw = decode_tile(sh, tile, tiles_per_group, kb_total);
@@ -146,22 +156,20 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
         const int t = tw.t;
         const int m0 = (t / sh.tiles_n) * kBlockM;
         const int n0 = (t % sh.tiles_n) * kBlockN;
-        for (int kb = tw.kb_begin; kb < tw.kb_end; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
+        for (int kb = tw.kb_begin; kb < tw.kb_end; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
             *abort_flag = 1;
             atomicCAS(sh.status, 0, (kDevTimeoutProducer << 24) | (it & 0xFFFFFF));
             ok = false;
             break;
           }
-          ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+          ptx::mbar_arrive_expect_tx(&full_bar[s], stage_bytes);
           const bool seg1 = kb >= sh.kb0;
           const int kk = (seg1 ? kb - sh.kb0 : kb) * kBlockK;
           const int mi = seg1 ? 1 : group;
           const CUtensorMap* ta = &maps.a[mi];
           const CUtensorMap* tb = &maps.b[mi];
-          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sa = smem + s * stage_bytes;
           uint8_t* sb = sa + kTileABytes;
           if (!sh.a_mn) {
             ptx::tma_load_2d(sa, ta, &full_bar[s], kk, m0);
@@ -184,14 +192,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      const uint32_t idesc = ptx::make_idesc_bf16(kBlockM, kBlockN, sh.a_mn, sh.b_mn);
+      const uint32_t idesc = ptx::make_idesc_bf16(kBlockM, sh.mma_n, sh.a_mn, sh.b_mn);
       // K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart; a k-step of 16
       // elements advances the start address by 32 bytes inside the swizzle span.
       // MN-major tile: boxes of 64 (mn) x 64 (k); 8-k groups 1024 bytes apart (SBO),
       // 64-wide mn groups one box (8192 bytes) apart (LBO); a k-step advances by 16 rows.
       const uint32_t a_lbo = sh.a_mn ? kMnBoxBytes : 0, a_step = sh.a_mn ? kUmmaK * 128 : kUmmaK * 2;
       const uint32_t b_lbo = sh.b_mn ? kMnBoxBytes : 0, b_step = sh.b_mn ? kUmmaK * 128 : kUmmaK * 2;
-      uint32_t it = 0, tcount = 0;
+      uint32_t it = 0, tcount = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
         const uint32_t acc = tcount & 1u;
@@ -204,9 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
         const TileWork tw = decode_tile(sh, tile, tiles_per_group, kb_total);
-        for (int kb = tw.kb_begin; kb < tw.kb_end; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
+        for (int kb = tw.kb_begin; kb < tw.kb_end; ++kb, ++it, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
           if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) {
             *abort_flag = 1;
             atomicCAS(sh.status, 0, (kDevTimeoutMma << 24) | (it & 0x7FFFFF));
@@ -214,7 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmMaps maps, const GemmShape sh, c
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t a_base = ptx::smem_u32(smem + s * kStageBytes);
+          const uint32_t a_base = ptx::smem_u32(smem + s * stage_bytes);
           const uint32_t b_base = a_base + kTileABytes;
 #pragma unroll
           for (int ks = 0; ks < kBlockK / kUmmaK; ++ks) {

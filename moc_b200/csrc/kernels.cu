@@ -952,6 +952,9 @@ int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
   const int frc = check_fuse(fuse, ldg, words);
   if (frc != kOk) return frc;
   prof_mark(kProfTopk, stream);
+  // bf16 rows with the forward fusion: the persistent shared-memory-staged kernel (any number of rows)
+  if (dtype == kBF16 && fuse && fuse->status && select_stream_supported(ldg, d_ffn, k, g, fuse->u_dense))
+    return launch_select_stream(g, ldg, tokens, d_ffn, k, *fuse, idx, g_sel, bitmap, rank0, fuse->status, stream);
   if (tokens <= 1024) {   // few rows: one CTA per row
     const size_t esz = dtype == kBF16 ? 2 : 4;
     const size_t smem = sizeof(uint32_t) * (kCtaSelBins + words) + esz * d_ffn;
@@ -974,9 +977,6 @@ int launch_topk_select(int dtype, void* g, int64_t ldg, int tokens, int d_ffn, i
     }
     return check_last("topk_select");
   }
-  // bf16 rows with the forward fusion: the persistent shared-memory-staged kernel
-  if (dtype == kBF16 && fuse && fuse->status && select_stream_supported(ldg, d_ffn, k, g, fuse->u_dense))
-    return launch_select_stream(g, ldg, tokens, d_ffn, k, *fuse, idx, g_sel, bitmap, rank0, fuse->status, stream);
   // bf16 fast path: needs aligned rows padded to the mask width
   if (dtype == kBF16 && ldg >= static_cast<int64_t>(words) * 32 && ldg % 8 == 0 &&
       (reinterpret_cast<uintptr_t>(g) & 15u) == 0) {

@@ -123,7 +123,7 @@ class SymmGradReducer(GradAllReducer):
     as a bucket (parameter dtype different from the compute dtype) fall back to the NCCL path of the base class.
     """
 
-    def __init__(self, group=None, average: bool = True, overlap: bool = True, reserve_sms: int = 16,
+    def __init__(self, group=None, average: bool = True, overlap: bool = True, reserve_sms: int = 8,
                  ctas: int | None = None, use_multicast: bool = True):
         super().__init__(group=group, average=average, overlap=overlap, reserve_sms=reserve_sms)
         self.use_multicast = use_multicast      # False: plain peer loads / stores even when a multicast mapping exists

@@ -1,7 +1,8 @@
-"""Gradient reduction by the library's own NVLink kernel (moc_symm_allreduce through moc_b200.dp.SymmGradReducer)
-on two GPUs: the reduced weight gradients of an MoC FFN must equal the mean of the two ranks' local gradients,
-in the multicast (in-switch) form and in the plain peer load/store form, over several steps in a row (the flag
-words are never reset between calls). Needs two GPUs; ranks are child processes, one per GPU."""
+"""Gradient reduction on two GPUs: the reduced weight gradients of an MoC FFN must equal the mean of the two ranks'
+local gradients - by the library's own NVLink kernel (moc_symm_allreduce through moc_b200.dp.SymmGradReducer) in
+the multicast (in-switch) form and in the plain peer load/store form, over several steps in a row (the flag words
+are never reset between calls), and by the NCCL path of moc_b200.dp.GradAllReducer (ReduceOp.AVG beside the dX
+GEMM). Needs two GPUs; ranks are child processes, one per GPU."""
 from __future__ import annotations
 
 import os
@@ -19,11 +20,11 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, use_multicast: bool, overlap: bool, out_dir: str):
+def _worker(rank: int, world: int, port: int, kind: str, overlap: bool, out_dir: str):
     import torch.distributed as dist
 
     import moc_b200
-    from moc_b200.dp import SymmGradReducer
+    from moc_b200.dp import GradAllReducer, SymmGradReducer
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -34,7 +35,11 @@ def _worker(rank: int, world: int, port: int, use_multicast: bool, overlap: bool
     d, d_ffn, k, tokens = 256, 1000, 200, 640
     torch.manual_seed(0)
     module = moc_b200.build_ffn(d, d_ffn, "moc", k=k).to(device=dev, dtype=torch.bfloat16)
-    reducer = SymmGradReducer(average=True, overlap=overlap, reserve_sms=16, use_multicast=use_multicast)
+    use_multicast = kind == "multicast"
+    if kind == "nccl":
+        reducer = GradAllReducer(average=True, overlap=overlap, reserve_sms=16)
+    else:
+        reducer = SymmGradReducer(average=True, overlap=overlap, reserve_sms=16, use_multicast=use_multicast)
     worst = 0.0
     for step in range(3):
         g = torch.Generator().manual_seed(100 * step + rank)
@@ -53,26 +58,28 @@ def _worker(rank: int, world: int, port: int, use_multicast: bool, overlap: bool
         with reducer:
             module(x).backward(dy)
         torch.cuda.synchronize()
-        reducer.check()
+        if kind != "nccl":
+            reducer.check()
         for p, w in zip(module.parameters(), want):
             err = float((p.grad.float() - w).norm() / w.norm().clamp_min(1e-30))
             worst = max(worst, err)
     # bf16 sums of two bf16 values are rounded once more than the fp32 mean: one part in 2^8
-    ok = worst <= 2.0 ** -7 and reducer.launched == 1 and (reducer.multicast or not use_multicast)
+    multicast = getattr(reducer, "multicast", None)
+    ok = worst <= 2.0 ** -7 and reducer.launched == 1 and (multicast or not use_multicast)
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
-        f.write(f"{int(ok)} worst={worst:.3e} multicast={reducer.multicast} launched={reducer.launched}\n")
+        f.write(f"{int(ok)} worst={worst:.3e} multicast={multicast} launched={reducer.launched}\n")
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_multicast,overlap", [(True, True), (False, True), (True, False)])
-def test_symmetric_gradient_reduction_two_gpus(use_multicast, overlap, tmp_path):
+@pytest.mark.parametrize("kind,overlap", [("multicast", True), ("peer", True), ("multicast", False), ("nccl", True)])
+def test_gradient_reduction_two_gpus(kind, overlap, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), use_multicast, overlap, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), kind, overlap, str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         line = (tmp_path / f"rank{r}.txt").read_text()
         assert line.startswith("1 "), line
