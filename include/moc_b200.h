@@ -215,6 +215,28 @@ int64_t moc_decode_static_max_batch(void);
 int64_t moc_decode_static_max_d(void);
 int64_t moc_decode_static_max_d_ffn(void);
 
+/* ---- host model: the non-FFN part of one static-cache decode step (bf16) -------------------------------------
+ * The reference's end-to-end decode benchmark (benchmarks/inference/benchmark_decode.py:312-362,
+ * DecoderModel.forward_step_static over the blocks of moc/model.py:19-88) leaves these to chains of small PyTorch
+ * operations; around a 22 us FFN they dominate the time of a token. Three launches per layer replace them. `pos`
+ * is a DEVICE pointer to the int64 position of the new token, so that a captured step can be replayed.
+ *
+ * moc_host_rmsnorm: h [rows, d] += delta (delta may be NULL: no update), then y = RMSNorm(h) * weight with the
+ *   statistics in fp32 (moc/model.py:19-27); h is updated in place. d % 8 == 0.
+ * moc_host_rope_cache: qkv [batch, 3, heads, head_dim] (one row of the fused projection per batch row);
+ *   q_out [batch, heads, head_dim] = rotary(q), cache_k[b, h, pos] = rotary(k), cache_v[b, h, pos] = v
+ *   (moc/model.py:37-43 on interleaved pairs; caches [batch, heads, t_max, head_dim];
+ *   cos_table, sin_table [t_max, head_dim / 2] bf16).
+ * moc_host_attn_step: y [batch, heads * head_dim] = softmax(q . K[0..pos] / sqrt(head_dim)) V[0..pos], fp32
+ *   accumulation (benchmark_decode.py:347-356). head_dim in {8, 16, 32, 64, 128}, t_max <= 11000. */
+int moc_host_rmsnorm(int64_t rows, int64_t d, void* h, const void* delta, const void* weight, void* y, float eps,
+                     void* stream);
+int moc_host_rope_cache(int64_t batch, int64_t heads, int64_t head_dim, int64_t t_max, const void* qkv,
+                        const void* cos_table, const void* sin_table, const int64_t* pos, void* q_out, void* cache_k,
+                        void* cache_v, void* stream);
+int moc_host_attn_step(int64_t batch, int64_t heads, int64_t head_dim, int64_t t_max, const void* q, const void* cache_k,
+                       const void* cache_v, const int64_t* pos, void* y, void* stream);
+
 /* Per-kernel timing without a profiler. Between moc_profile_begin and moc_profile_end (process-wide,
  * one profile at a time) the library records events[0], events[1], ... (a HOST array of created
  * cudaEvent_t handles, timing enabled) on the stream of each call, one right before every

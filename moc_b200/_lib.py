@@ -43,6 +43,9 @@ SIGNATURES = {
     "moc_set_overlap_sm_reserve": (c_int, [c_int]),
     "moc_symm_allreduce": (c_int, [c_int, c_int, c_int, _P, _P, _P, c_int64, c_int, ctypes.c_uint32, c_int, _P]),
     "moc_symm_allreduce_flag_bytes": (c_int64, []),
+    "moc_host_rmsnorm": (c_int, [c_int64, c_int64, _P, _P, _P, _P, ctypes.c_float, _P]),
+    "moc_host_rope_cache": (c_int, [c_int64] * 4 + [_P] * 8),
+    "moc_host_attn_step": (c_int, [c_int64] * 4 + [_P] * 6),
     "moc_symm_allreduce_status": (c_int, [_P, _P]),
     "moc_read_status": (c_int, [_P, _P]),
     "moc_publish_status": (c_int, [_P, _P, _P]),

@@ -20,7 +20,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 INCLUDE = PKG_DIR.parent / "include"
 LIB_PATH = PKG_DIR / "libmoc_b200.so"
-SOURCES = ["api.cu", "gemm.cu", "kernels.cu", "decode.cu", "decode_stream.cu", "select_stream.cu", "allreduce.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "gemm.cu", "kernels.cu", "decode.cu", "decode_stream.cu", "select_stream.cu", "allreduce.cu", "host_step.cu", "noalloc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

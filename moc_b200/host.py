@@ -21,6 +21,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import _lib
 from .ffn import build_ffn
 from .inference import InferenceMoCSwiGLUFFN
 
@@ -249,6 +250,9 @@ class GreedyDecoder:
             f.freeze_for_compile()
             self.ffn.append(f)
         self._graph = None
+        self._rope_bf16 = None
+        # graph-replayed steps use the library's fused host-step kernels when the model allows (bf16, supported head size)
+        self.fused_host_step = True
 
     @torch.no_grad()
     def _forward(self, ids, first_pos: int):
@@ -273,6 +277,55 @@ class GreedyDecoder:
             h = h + self.ffn[i](blk.ffn_norm(h).reshape(b, d), mode=ffn_mode).reshape(b, 1, d)
         return m._logits(h)[:, 0].argmax(dim=-1)
 
+    def _fused_step_supported(self) -> bool:
+        cfg = self.model.config
+        hd = cfg.hidden_size // cfg.num_attention_heads
+        w = self.model.tok_emb.weight
+        return (w.is_cuda and w.dtype == torch.bfloat16 and cfg.hidden_size % 8 == 0 and hd in (8, 16, 32, 64, 128)
+                and cfg.max_seq_len <= 11000 and _lib.exported("moc_host_attn_step"))
+
+    @torch.no_grad()
+    def _step_fused(self, ids, pos):
+        """The same step as _step with the operations around the projections done by the library's host-step
+        kernels (moc_host_rmsnorm, moc_host_rope_cache, moc_host_attn_step): per layer two fused residual + norm
+        launches, one rotary + cache launch and one attention launch instead of about 45 framework kernels. The
+        QKV, output and LM-head projections stay PyTorch matrix products, the FFN is the decode entry point."""
+        lib = _lib.lib()
+        m = self.model
+        cfg = m.config
+        heads, hd, t_max = cfg.num_attention_heads, cfg.hidden_size // cfg.num_attention_heads, cfg.max_seq_len
+        h = m.tok_emb(ids)[:, 0].contiguous()                     # [b, d], updated in place below
+        b, d = h.shape
+        stream = _lib.stream_ptr(h.device)
+        if self._rope_bf16 is None:
+            a0 = m.blocks[0].attn
+            self._rope_bf16 = (a0.rope_cos.to(h.dtype).contiguous(), a0.rope_sin.to(h.dtype).contiguous())
+        cos, sin = self._rope_bf16
+        y = torch.empty_like(h)
+        q = torch.empty(b, heads * hd, device=h.device, dtype=h.dtype)
+        att = torch.empty_like(q)
+        ffn_mode = "dense_baseline" if m.ffn_type == "dense" else self.mode
+        delta = None
+        with torch.cuda.device(h.device):
+            for i, blk in enumerate(m.blocks):
+                _lib.check(lib.moc_host_rmsnorm(b, d, h.data_ptr(), _lib.ptr(delta), blk.attn_norm.weight.data_ptr(),
+                                                y.data_ptr(), blk.attn_norm.eps, stream), "moc_host_rmsnorm")
+                qkv = blk.attn.qkv_proj(y)                        # [b, 3 d] = [b, 3, heads, hd]
+                _lib.check(lib.moc_host_rope_cache(b, heads, hd, t_max, qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                                   pos.data_ptr(), q.data_ptr(), self.cache_k[i].data_ptr(),
+                                                   self.cache_v[i].data_ptr(), stream), "moc_host_rope_cache")
+                _lib.check(lib.moc_host_attn_step(b, heads, hd, t_max, q.data_ptr(), self.cache_k[i].data_ptr(),
+                                                  self.cache_v[i].data_ptr(), pos.data_ptr(), att.data_ptr(), stream),
+                           "moc_host_attn_step")
+                o = blk.attn.out_proj(att)
+                _lib.check(lib.moc_host_rmsnorm(b, d, h.data_ptr(), o.data_ptr(), blk.ffn_norm.weight.data_ptr(),
+                                                y.data_ptr(), blk.ffn_norm.eps, stream), "moc_host_rmsnorm")
+                delta = self.ffn[i](y, mode=ffn_mode)
+            _lib.check(lib.moc_host_rmsnorm(b, d, h.data_ptr(), _lib.ptr(delta), m.norm.weight.data_ptr(), y.data_ptr(),
+                                            m.norm.eps, stream), "moc_host_rmsnorm")
+        logits = y @ m.tok_emb.weight.t() if m.lm_head is None else m.lm_head(y)
+        return logits.argmax(dim=-1)
+
     @torch.no_grad()
     def generate_graphed(self, prompt_ids, new_tokens: int):
         """Like generate(), with every decode step after the prompt replayed from one CUDA graph: the token ids,
@@ -289,8 +342,10 @@ class GreedyDecoder:
         pos = torch.full((1,), t0, dtype=torch.int64, device=dev)
         slot = torch.ones(1, dtype=torch.int64, device=dev)
 
+        step = self._step_fused if (self.fused_host_step and self._fused_step_supported()) else self._step
+
         def body():
-            nxt = self._step(ids, pos)
+            nxt = step(ids, pos)
             out.index_copy_(1, slot, nxt[:, None])
             ids.copy_(nxt[:, None])
             pos.add_(1)

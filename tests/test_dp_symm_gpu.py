@@ -83,3 +83,38 @@ def test_gradient_reduction_two_gpus(kind, overlap, tmp_path):
     for r in range(world):
         line = (tmp_path / f"rank{r}.txt").read_text()
         assert line.startswith("1 "), line
+
+
+def test_wait_for_an_absent_rank_runs_out_and_is_reported():
+    """One GPU plays rank 0 of a two-rank reduction whose rank 1 never shows up (its buffer and flag words are local
+    stand-ins that nothing ever signals): the kernel's bounded wait runs out after about a second, the kernel returns,
+    moc_symm_allreduce_status reports MOC_ERR_DEVICE_TIMEOUT, and a following one-rank call on fresh flags works.
+    Nothing traps or spins without limit."""
+    import ctypes
+    import time
+
+    from moc_b200 import _lib
+
+    lib = _lib.lib()
+    dev = torch.device("cuda:0")
+    n = 4096
+    bufs = [torch.ones(n, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    nflag = lib.moc_symm_allreduce_flag_bytes() // 4
+    flags = [torch.zeros(nflag, device=dev, dtype=torch.int32) for _ in range(2)]
+    ptrs = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+    fptrs = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+    stream = _lib.stream_ptr()
+    t0 = time.perf_counter()
+    _lib.check(lib.moc_symm_allreduce(0, 0, 2, ptrs, None, fptrs, n * 2, 1, 1, 4, stream), "moc_symm_allreduce")
+    rc = lib.moc_symm_allreduce_status(flags[0].data_ptr(), stream)
+    took = time.perf_counter() - t0
+    assert rc == _lib.ERR_DEVICE_TIMEOUT and "timed out" in _lib.last_error(), (rc, _lib.last_error())
+    assert took < 20.0, took
+    # the device is still usable: a one-rank mean over fresh flags leaves the values as they are
+    solo = torch.full((n,), 3.0, device=dev, dtype=torch.bfloat16)
+    f1 = torch.zeros(nflag, device=dev, dtype=torch.int32)
+    p1 = (ctypes.c_void_p * 1)(solo.data_ptr())
+    q1 = (ctypes.c_void_p * 1)(f1.data_ptr())
+    _lib.check(lib.moc_symm_allreduce(0, 0, 1, p1, None, q1, n * 2, 1, 1, 4, stream), "moc_symm_allreduce")
+    assert lib.moc_symm_allreduce_status(f1.data_ptr(), stream) == 0
+    assert bool((solo == 3.0).all())
