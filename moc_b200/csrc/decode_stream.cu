@@ -180,6 +180,11 @@ __device__ __forceinline__ uint32_t stream_exscan(uint32_t v, int lane) {
 // only before it first touches the workspace.
 __global__ void __launch_bounds__(256) decode_stream_clear_kernel(int4* __restrict__ area, int n16) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // This kernel is itself launched as a programmatic dependent of whatever kernel precedes it in the stream: when
+  // that is the persistent kernel of the previous decode call (which lets its dependents be scheduled as soon as it
+  // starts), the launch latency of this call hides behind that call. The previous call may use the same workspace,
+  // so nothing is touched before it has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x)
     area[i] = make_int4(0, 0, 0, 0);
 }
@@ -187,6 +192,8 @@ __global__ void __launch_bounds__(256) decode_stream_clear_kernel(int4* __restri
 __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(const StreamArgs a) {
   extern __shared__ __align__(128) uint8_t ssm[];
   __shared__ StreamShared sh;
+  // the clear kernel of a following decode call may be scheduled now (it waits for this grid to complete)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int batch = a.batch, d = a.d, F = a.d_ffn, cpc = a.cpc, rule = a.rule;
   const uint32_t pitch = stream_pitch(d);
@@ -822,7 +829,35 @@ int launch_decode_stream(int rule, int batch, int d, int d_ffn, int k, const voi
   }
   const size_t clear = 256 + (rule == 0 ? static_cast<size_t>(batch) * kSBins * 4 : 0);
   const int n16 = static_cast<int>(clear / 16);
-  decode_stream_clear_kernel<<<rule == 0 ? 8 : 1, 256, 0, stream>>>(reinterpret_cast<int4*>(status_area), n16);
+  static std::atomic<int> clear_pdl{-1};   // 1: the clear kernel is launched as a programmatic dependent
+  int cmode = clear_pdl.load(std::memory_order_relaxed);
+  if (cmode < 0) {
+    const char* e = getenv("MOC_B200_DECODE_PDL");
+    cmode = (e && e[0] == '0') ? 0 : 1;
+    clear_pdl.store(cmode, std::memory_order_relaxed);
+  }
+  {
+    cudaLaunchConfig_t ccfg = {};
+    ccfg.gridDim = dim3(rule == 0 ? 8 : 1);
+    ccfg.blockDim = dim3(256);
+    ccfg.stream = stream;
+    cudaLaunchAttribute cattr[1];
+    cattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    cattr[0].val.programmaticStreamSerializationAllowed = 1;
+    ccfg.attrs = cattr;
+    ccfg.numAttrs = cmode ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&ccfg, decode_stream_clear_kernel, reinterpret_cast<int4*>(status_area), n16);
+    if (err != cudaSuccess && cmode) {
+      cudaGetLastError();
+      clear_pdl.store(0, std::memory_order_relaxed);
+      ccfg.numAttrs = 0;
+      err = cudaLaunchKernelEx(&ccfg, decode_stream_clear_kernel, reinterpret_cast<int4*>(status_area), n16);
+    }
+    if (err != cudaSuccess) {
+      set_error("decode_stream clear launch: %s", cudaGetErrorString(err));
+      return kErrCuda;
+    }
+  }
   int rc = check_last("decode_stream clear");
   if (rc != kOk) return rc;
   const size_t smem = stream_stage_bytes(batch, d, d_ffn) + kSRedBytes;
