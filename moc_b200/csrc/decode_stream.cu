@@ -80,7 +80,7 @@ struct StreamArgs {
 };
 
 struct StreamShared {
-  uint64_t full[kSStages], empty[kSStages], bar_rows, bar_ent;
+  uint64_t full[kSStages], empty[kSStages], bar_rows, bar_ent, bar_thr;
   int abort, ok;
   uint32_t n_ent;
   uint16_t g_own[kSNB][kSMaxCh];       // bf16 bits of the own gate scores
@@ -216,6 +216,7 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(const Strea
     }
     ptx::mbar_init(&sh.bar_rows, 1);
     ptx::mbar_init(&sh.bar_ent, 1);
+    ptx::mbar_init(&sh.bar_thr, 1);
     sh.abort = 0;
     sh.ok = 1;
     sh.n_ent = 0;
@@ -261,6 +262,22 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(const Strea
       put_tile(nrows, w + static_cast<int64_t>(ch0 + t * kSTile + (lane < nrows ? lane : 0)) * d);
     }
     if (rule == 2) return;
+    if (rule == 0) {
+      // Top-K rule: as soon as the threshold BIN of every row is known, the own channels whose key lies in a
+      // higher bin are certainly selected. Their W_up and W_down^T rows are requested into L2 now, while the
+      // consumers still resolve the exact threshold and the ties (a few microseconds), so that the copies issued
+      // after the selection find them there. Channels inside the threshold bin (a few percent) are left alone.
+      if (stream_mbar_wait(&sh.bar_thr, 0u, abort_flag, 8 * limit)) {
+        for (int lc = lane; lc < ncl; lc += 32) {
+          bool certain = false;
+          for (int b = 0; b < batch; ++b) certain = certain || (order_key16(sh.g_own[b][lc]) >> 5) > sh.d1[b];
+          if (certain) {
+            ptx::bulk_prefetch_l2(a.w_up + static_cast<int64_t>(ch0 + lc) * d, row_bytes);
+            ptx::bulk_prefetch_l2(a.w_down_t + static_cast<int64_t>(ch0 + lc) * d, row_bytes);
+          }
+        }
+      }
+    }
     // the entry list of this CTA (written by the consumers after selection)
     if (!stream_mbar_wait(&sh.bar_ent, 0u, abort_flag, 8 * limit)) {
       if (lane == 0) {
@@ -397,6 +414,7 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(const Strea
           if (F + lane < static_cast<int>(rowpad)) srow[warp * rowpad + F + lane] = static_cast<uint16_t>(~pat);
         }
         consumer_sync();
+        if (tid == 0) ptx::mbar_arrive(&sh.bar_thr);   // the producer warp may prefetch the certain rows
         // One vectorised pass over the score rows collects the keys of each row's threshold bin (a few percent
         // of a row) as (channel, lower 5 key bits) candidates in one flat list per row; the rest works on these
         // short lists. The 16 warps split the rows (16 / batch' warps per row); a warp places the hits of its 32

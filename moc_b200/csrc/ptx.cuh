@@ -98,6 +98,12 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
                : "memory");
 }
 
+// Request of a contiguous global range into L2 (no destination, no completion to wait for); address 16-byte
+// aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
 // Untiled bulk copy shared -> global, tracked by the bulk async-group of the issuing thread; both addresses
 // 16-byte aligned, size a multiple of 16. Shared-memory writes made with ordinary stores must be ordered
 // before it by fence_proxy_async_smem() in the writing threads and a barrier.

@@ -15,6 +15,7 @@ the CPU tests of the bookkeeping).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -142,6 +143,8 @@ class SymmGradReducer(GradAllReducer):
         self.multicast = None
 
     def _alloc(self, numel: int, dtype: torch.dtype, device) -> tuple:
+        if os.environ.get("MOC_B200_SYMM_DISABLE") == "1":     # lets a caller exercise its fallback path
+            raise RuntimeError("symmetric memory disabled by MOC_B200_SYMM_DISABLE=1")
         t = self._symm.empty(numel, dtype=dtype, device=device)
         return t, self._symm.rendezvous(t, self._group)
 
