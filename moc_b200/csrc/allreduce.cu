@@ -38,7 +38,6 @@ constexpr int kArStatus = 66;    // local: nonzero after a time-out
 constexpr uint32_t kArAbortBit = 0x80000000u;   // in the go word: this call gave up (call numbers stay below 2^31)
 
 struct ArArgs {
-  void* local;                        // this rank's buffer (same as peer[rank])
   void* mc;                           // multicast address of the buffer, or null
   void* peer[kArMaxWorld];            // every rank's buffer as mapped here
   uint32_t* flags[kArMaxWorld];       // every rank's flag words as mapped here
@@ -281,7 +280,6 @@ int moc_symm_allreduce(int dtype, int rank, int world, void* const* peer_buffers
     a.peer[r] = peer_buffers[r];
     a.flags[r] = static_cast<uint32_t*>(peer_flags[r]);
   }
-  a.local = peer_buffers[rank];
   a.mc = multicast_buffer;
   a.vecs = bytes / 16;
   a.wait_cycles = 2000000000LL;   // about one second
