@@ -124,9 +124,9 @@ __device__ __forceinline__ bool stream_grid_barrier(unsigned* counter, unsigned 
   consumer_sync();
   if (threadIdx.x == 0) {
     int ok = 1;
-    // arrival: a reduction with release semantics (no return value to wait for). The release is cumulative: it
-    // also orders what the other threads of the CTA wrote before the CTA barrier above, so no separate fence is
-    // needed. The polls are relaxed loads; one acquire fence follows the successful one.
+    // arrival: a reduction with release semantics (no return value to wait for); it also publishes what the other
+    // threads of the CTA wrote before the barrier above
+    __threadfence();
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(counter), "r"(1u) : "memory");
     const long long t0 = clock64();
     while (true) {
@@ -137,10 +137,9 @@ __device__ __forceinline__ bool stream_grid_barrier(unsigned* counter, unsigned 
         break;
       }
       unsigned v;
-      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
       if (v >= target) break;
     }
-    asm volatile("fence.acq_rel.gpu;" ::: "memory");
     sh.ok = ok;
     if (!ok) sh.abort = 1;
   }
