@@ -80,6 +80,19 @@ def test_tcgen05_gemm_transposed_store(impl, m, n, k):
     torch.testing.assert_close(got, ref.bfloat16().float(), rtol=2 ** -7, atol=2e-2)
 
 
+@pytest.mark.parametrize("c_t", [0, 1])
+@pytest.mark.parametrize("a_mn", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(5461, 64, 2048), (300, 40, 200), (257, 100, 320), (129, 128, 64), (2048, 9, 5461),
+                                   (700, 16, 72)])
+def test_tcgen05_gemm_few_columns(m, n, k, a_mn, c_t):
+    """Products with at most 128 columns and a K-major B (the decode projections: weights as the M operand, batch
+    rows as N) run on the single-CTA kernel with an MMA and a B tile as narrow as N allows and a deeper operand
+    ring."""
+    got, ref = _run_gemm(torch.bfloat16, 3, m, n, k, a_mn, 0, c_t, seed=m + n)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, ref.bfloat16().float(), rtol=2 ** -7, atol=1e-2 * max(1.0, (k / 64) ** 0.5))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("a_mn,b_mn,c_t", [(0, 0, 0), (0, 1, 0), (1, 1, 1)])
 def test_simt_gemm(dtype, a_mn, b_mn, c_t):
